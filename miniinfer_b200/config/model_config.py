@@ -142,3 +142,122 @@ class Qwen3Config(ModelConfig):
       return int(self.sliding_window) if self.layer_types[layer] == "sliding_attention" else None
     first = self.max_window_layers if self.max_window_layers is not None else 0
     return int(self.sliding_window) if layer >= first else None
+
+
+@dataclass
+class RikanexMixerConfig:
+  """The attention of one Rikanex layer (``layers[i].mixer``)."""
+
+  heads: int
+  kv_heads: int
+  dim: int                      # query / key size of a head
+  vdim: int                     # value size of a head
+  scale: float                  # the scores' factor
+  window: Optional[int]         # ``mask.size``: token i sees j with 0 <= i - j < window; None: every earlier token
+  v_mix: bool                   # values mixed with those of the first layer that says so
+
+
+@dataclass
+class RikanexMlpConfig:
+  """The feed-forward of one Rikanex layer (``layers[i].mlp``): ``kind`` dense (``ff``) or moe (``ff`` of an expert,
+  ``experts``, ``top``)."""
+
+  kind: str
+  ff: int
+  experts: int = 0
+  top: int = 0
+
+
+@dataclass
+class RikanexConfig(ModelConfig):
+  """Rikanex: a decoder of parallel layers (one layer norm, attention and feed-forward side by side), windowed
+  attention with a sink and an output gate, dense or routed feed-forwards.  ``config.json`` keys: ``architecture``,
+  ``vocab``, ``width``, ``embedding.scale``, ``norm.eps``, ``layers[i].{type, mixer, mlp}``; the layers may differ in
+  every size.  The design has no position limit of its own; ``max_position_embeddings`` is only the engine's bound."""
+
+  architecture: str = "Rikanex"
+  vocab: int = 0
+  width: int = 0
+  embedding: Dict[str, Any] = field(default_factory=dict)
+  norm: Dict[str, Any] = field(default_factory=dict)
+  layers: List[Dict[str, Any]] = field(default_factory=list)
+  max_position_embeddings: int = 1 << 30
+  initializer_range: float = 0.02
+
+  def validate(self) -> None:
+    if not self.architectures:
+      self.architectures = [self.architecture]
+    self.vocab_size = self.vocab
+    for key in ("vocab", "width"):
+      v = getattr(self, key)
+      if not isinstance(v, int) or v <= 0:
+        raise ConfigError(f"{key} must be a positive integer, got {v!r}")
+    if not isinstance(self.embedding.get("scale"), (int, float)):
+      raise ConfigError("embedding.scale must be a number")
+    eps = self.norm.get("eps")
+    if not isinstance(eps, (int, float)) or not eps > 0:
+      raise ConfigError(f"norm.eps must be a positive number, got {eps!r}")
+    if not self.layers:
+      raise ConfigError("layers must list at least one layer")
+    for i in range(len(self.layers)):
+      self.mixer_of(i)
+      self.mlp_of(i)
+
+  @property
+  def embedding_scale(self) -> float:
+    return float(self.embedding["scale"])
+
+  @property
+  def norm_eps(self) -> float:
+    return float(self.norm["eps"])
+
+  def mixer_of(self, i: int) -> RikanexMixerConfig:
+    layer = self.layers[i]
+    if layer.get("type") != "attention":
+      raise ConfigError(f"layers[{i}].type={layer.get('type')!r} is not a mixer of this design (known: 'attention')")
+    m = layer.get("mixer")
+    if not isinstance(m, dict):
+      raise ConfigError(f"layers[{i}].mixer is missing")
+    for key in ("heads", "kv_heads", "dim", "vdim"):
+      v = m.get(key)
+      if not isinstance(v, int) or v <= 0:
+        raise ConfigError(f"layers[{i}].mixer.{key} must be a positive integer, got {v!r}")
+    if m["heads"] % m["kv_heads"]:
+      raise ConfigError(f"layers[{i}].mixer.heads={m['heads']} must be a multiple of kv_heads={m['kv_heads']}")
+    if not isinstance(m.get("scale"), (int, float)):
+      raise ConfigError(f"layers[{i}].mixer.scale must be a number")
+    mask = m.get("mask")
+    window = None
+    if mask is not None:
+      window = mask.get("size") if isinstance(mask, dict) else None
+      if not isinstance(window, int) or window <= 0:
+        raise ConfigError(f"layers[{i}].mixer.mask.size must be a positive integer, got {mask!r}")
+    return RikanexMixerConfig(m["heads"], m["kv_heads"], m["dim"], m["vdim"], float(m["scale"]), window, bool(m.get("v_mix", False)))
+
+  def mlp_of(self, i: int) -> Optional[RikanexMlpConfig]:
+    mlp = self.layers[i].get("mlp")
+    if mlp is None:
+      return None
+    kind = mlp.get("kind")
+    if kind == "dense":
+      ff = mlp.get("ff")
+      if not isinstance(ff, int) or ff <= 0:
+        raise ConfigError(f"layers[{i}].mlp.ff must be a positive integer, got {ff!r}")
+      return RikanexMlpConfig("dense", ff)
+    if kind == "moe":
+      ff = (mlp.get("expert") or {}).get("ff")
+      router = mlp.get("router") or {}
+      experts, top = router.get("experts"), router.get("top")
+      for key, v in (("expert.ff", ff), ("router.experts", experts), ("router.top", top)):
+        if not isinstance(v, int) or v <= 0:
+          raise ConfigError(f"layers[{i}].mlp.{key} must be a positive integer, got {v!r}")
+      if top > experts:
+        raise ConfigError(f"layers[{i}].mlp.router.top={top} is more than experts={experts}")
+      return RikanexMlpConfig("moe", ff, experts, top)
+    raise ConfigError(f"layers[{i}].mlp.kind={kind!r} is not known (dense, moe)")
+
+  def to_dict(self) -> Dict[str, Any]:
+    d = {"architecture": self.architecture, "vocab": self.vocab, "width": self.width, "embedding": dict(self.embedding),
+         "norm": dict(self.norm), "layers": [dict(x) for x in self.layers]}
+    d.update(self.extra)
+    return d

@@ -53,10 +53,15 @@ def lookup(name: str) -> Tuple[Type[ModelConfig], Callable]:
 
 
 def architecture_of(config_dict: dict) -> str:
+  """The name a configuration is registered under: the first entry of ``architectures``, or ``architecture`` (a
+  string) in files that name one."""
   archs = config_dict.get("architectures")
-  if not archs:
-    raise ConfigError("config.json has no 'architectures' entry")
-  return archs[0]
+  if archs:
+    return archs[0]
+  name = config_dict.get("architecture")
+  if isinstance(name, str) and name:
+    return name
+  raise ConfigError("config.json has neither an 'architectures' nor an 'architecture' entry")
 
 
 def load_model_config(model_dir: str) -> ModelConfig:

@@ -21,6 +21,10 @@
 // Stands where the reference calls FlashInfer's / FlashAttention's decode kernels
 // (miniinfer/layers/attention_backend/flashinfer_backend.py:323-327).
 //
+// Options (off when null): a sink per query head joins the denominator once, in the merge of the chunks
+// (exp(sink), unscaled, no value); an output gate multiplies the output row with sigmoid(gate[token,
+// head, :]); out_hd < head size writes only the first out_hd values of a head (padded cache rows).
+//
 // Compiled once per head size: -DMI_HEAD_DIM=<multiple of 16, 16..256>.
 #include "common.cuh"
 
@@ -82,6 +86,9 @@ struct DecodeArgs {
   int* counters;                 // [n_dec, nkv], zero between launches
   int nh, nkv, page_size, window, chunk, max_splits;
   float scale;
+  const float* sink;             // [nh] or null
+  const __nv_bfloat16* gate;     // [T, gate_stride], head h at h * out_hd; or null
+  int gate_stride, out_hd;
 };
 
 // Gathers keys first .. first + BK of one kv head (K and V rows) into a stage; rows from `end` on are
@@ -318,6 +325,8 @@ decode_split_kernel(DecodeArgs a) {
     float m = -INFINITY;
     for (int s = lane; s < n_splits; s += 32) m = fmaxf(m, __ldcg(ml + 2 * s));
     m = mi::warp_max(m);
+    const float sink2 = a.sink ? a.sink[head] * 1.4426950408889634f : -INFINITY;   // base-2 domain, like the scores
+    m = fmaxf(m, sink2);
     float l = 0.f, w_lane = 0.f;
     for (int s = lane; s < n_splits; s += 32) {
       const float f = exp2f(__ldcg(ml + 2 * s) - m);
@@ -325,6 +334,7 @@ decode_split_kernel(DecodeArgs a) {
       l = fmaf(__ldcg(ml + 2 * s + 1), f, l);
     }
     l = mi::warp_sum(l);
+    if (a.sink) l += exp2f(sink2 - m);
     const float inv = 1.f / l;
     float acc = 0.f;
     const int first = min(n_splits, 32);
@@ -337,7 +347,11 @@ decode_split_kernel(DecodeArgs a) {
       const float f = exp2f(__ldcg(ml + 2 * s) - m);
       if (d < HD) acc = fmaf(__ldcg(po + (size_t)s * HD + d), f, acc);
     }
-    if (d < HD) a.out[(size_t)row * a.nh * HD + (size_t)head * HD + d] = __float2bfloat16_rn(acc * inv);
+    if (d < a.out_hd) {
+      float y = acc * inv;
+      if (a.gate) y = __fdividef(y, 1.f + __expf(-__bfloat162float(a.gate[(size_t)row * a.gate_stride + (size_t)head * a.out_hd + d])));
+      a.out[((size_t)row * a.nh + head) * a.out_hd + d] = __float2bfloat16_rn(y);
+    }
   }
 }
 
@@ -357,7 +371,9 @@ MI_API int mi_attention_decode_bf16(void* out, const void* q_base, int q_stride,
                                     const int* block_table, int bt_stride, const int* decode_items,
                                     const int* q_start, const int* ctx_len, const int* seq_slot, float* scratch,
                                     int* counters, int n_dec, int nh, int nkv, int page_size, float scale,
-                                    int window, int chunk, int max_splits, cudaStream_t stream) {
+                                    int window, int chunk, int max_splits, const float* sink, const void* gate,
+                                    int gate_stride, int out_hd, cudaStream_t stream) {
+  MI_REQUIRE(out_hd > 0 && out_hd <= HD, "attention_decode: out_hd=%d must lie in 1..%d", out_hd, HD);
   MI_REQUIRE(n_dec >= 0 && nh > 0 && nkv > 0 && nh % nkv == 0, "attention_decode: bad head counts nh=%d nkv=%d", nh, nkv);
   MI_REQUIRE(chunk >= BK && chunk <= MAX_CHUNK && chunk % BK == 0, "attention_decode: chunk=%d must be a multiple of %d up to %d", chunk, BK, MAX_CHUNK);
   MI_REQUIRE(max_splits >= 1 && max_splits <= 65535, "attention_decode: max_splits=%d", max_splits);
@@ -381,6 +397,7 @@ MI_API int mi_attention_decode_bf16(void* out, const void* q_base, int q_stride,
   a.counters = counters;
   a.nh = nh; a.nkv = nkv; a.page_size = page_size; a.window = window; a.chunk = chunk; a.max_splits = max_splits;
   a.scale = scale;
+  a.sink = sink; a.gate = (const __nv_bfloat16*)gate; a.gate_stride = gate_stride; a.out_hd = out_hd;
   static bool configured = false;
   if (!configured) {
     cudaError_t err = cudaFuncSetAttribute(decode_split_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES);

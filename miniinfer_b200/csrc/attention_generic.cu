@@ -14,6 +14,12 @@
 //
 // Cache layout of one layer: [page, 2 (k, v), kv head, token in page, head_dim]; the keys of this
 // step's own tokens are already in it (the QKV pass stores them first).
+//
+// Three options, all off when their pointers are null: a sink per query head - a learned logit whose
+// exponential joins the softmax's denominator once, unscaled, with no key and no value (the running
+// maximum starts at the sink and the running sum at 1); an output gate - the output row is multiplied
+// element by element with sigmoid(gate[token, head, :]); and out_hd < head_dim - only the first out_hd
+// values of a head are written (the cache rows are padded).
 #include "common.cuh"
 
 namespace {
@@ -59,7 +65,8 @@ attention_generic_kernel(T* __restrict__ out, const T* __restrict__ q_base, int 
                          const T* __restrict__ kv_layer, const int* __restrict__ block_table, int bt_stride,
                          const int* __restrict__ token_item, const int* __restrict__ positions,
                          const int* __restrict__ seq_slot, int nh, int nkv, int hd, int page_size,
-                         float scale, int window) {
+                         float scale, int window, const float* __restrict__ sink, const T* __restrict__ gate,
+                         int gate_stride, int out_hd) {
   mi::grid_dependency_sync();
   __shared__ float qs[WARPS][MAX_HD];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -84,6 +91,7 @@ attention_generic_kernel(T* __restrict__ out, const T* __restrict__ q_base, int 
 #pragma unroll
   for (int i = 0; i < MAX_HD / 32; ++i) o[i] = 0.f;
   float m = -INFINITY, l = 0.f;
+  if (sink) { m = sink[head]; l = 1.f; }
 
   for (int c = (lo / 32) * 32; c <= p; c += 32) {
     const int j = c + lane;
@@ -115,11 +123,16 @@ attention_generic_kernel(T* __restrict__ out, const T* __restrict__ q_base, int 
     }
   }
   const float inv = 1.f / l;
-  T* dst = out + (size_t)tkn * nh * hd + (size_t)head * hd;
+  T* dst = out + ((size_t)tkn * nh + head) * out_hd;
+  const T* gt = gate ? gate + (size_t)tkn * gate_stride + (size_t)head * out_hd : nullptr;
 #pragma unroll
   for (int i = 0; i < MAX_HD / 32; ++i) {
     const int d = lane + 32 * i;
-    if (d < hd) dst[d] = mi::from_float<T>(o[i] * inv);
+    if (d < out_hd) {
+      float y = o[i] * inv;
+      if (gt) y = y / (1.f + expf(-mi::to_float(gt[d])));
+      dst[d] = mi::from_float<T>(y);
+    }
   }
 }
 
@@ -129,7 +142,9 @@ attention_generic_kernel(T* __restrict__ out, const T* __restrict__ q_base, int 
 MI_API int mi_attention_generic(void* out, const void* q_base, int q_stride, int dtype, const void* kv_layer,
                                 const int* block_table, int bt_stride, const int* token_item,
                                 const int* positions, const int* seq_slot, int T, int nh, int nkv, int hd,
-                                int page_size, float scale, int window, cudaStream_t stream) {
+                                int page_size, float scale, int window, const float* sink, const void* gate,
+                                int gate_stride, int out_hd, cudaStream_t stream) {
+  MI_REQUIRE(out_hd > 0 && out_hd <= hd, "attention: out_hd=%d must lie in 1..head_dim", out_hd);
   MI_REQUIRE(T >= 0 && nh > 0 && nkv > 0 && nh % nkv == 0, "attention: bad head counts nh=%d nkv=%d", nh, nkv);
   MI_REQUIRE(hd > 0 && hd % 4 == 0 && hd <= MAX_HD, "attention: head_dim=%d must be a multiple of 4 up to %d", hd, MAX_HD);
   MI_REQUIRE(page_size > 0 && q_stride % 4 == 0, "attention: bad page_size=%d or q_stride=%d", page_size, q_stride);
@@ -139,11 +154,12 @@ MI_API int mi_attention_generic(void* out, const void* q_base, int q_stride, int
   if (dtype == MI_BF16)
     mi::launch(attention_generic_kernel<__nv_bfloat16>, dim3(grid), dim3(WARPS * 32), 0, stream, 
         (__nv_bfloat16*)out, (const __nv_bfloat16*)q_base, q_stride, (const __nv_bfloat16*)kv_layer, block_table,
-        bt_stride, token_item, positions, seq_slot, nh, nkv, hd, page_size, scale, window);
+        bt_stride, token_item, positions, seq_slot, nh, nkv, hd, page_size, scale, window, sink, (const __nv_bfloat16*)gate,
+        gate_stride, out_hd);
   else if (dtype == MI_F32)
     mi::launch(attention_generic_kernel<float>, dim3(grid), dim3(WARPS * 32), 0, stream, 
         (float*)out, (const float*)q_base, q_stride, (const float*)kv_layer, block_table, bt_stride, token_item,
-        positions, seq_slot, nh, nkv, hd, page_size, scale, window);
+        positions, seq_slot, nh, nkv, hd, page_size, scale, window, sink, (const float*)gate, gate_stride, out_hd);
   else
     return mi_fail("attention: unknown dtype %d", dtype);
   MI_LAUNCH_OK("attention_generic");

@@ -17,6 +17,10 @@
 // (miniinfer/layers/attention_backend/flashattention_backend.py:441-452,
 // flashinfer_backend.py:352-374).
 //
+// Options (off when null): a sink per query head joins the softmax's denominator once, at the end
+// (exp(sink), unscaled, no value); an output gate multiplies the output row with sigmoid(gate[token,
+// head, :]); out_hd < head size writes only the first out_hd values of a head (padded cache rows).
+//
 // Compiled once per head size: -DMI_HEAD_DIM=<multiple of 16, 16..256>.
 #include "common.cuh"
 
@@ -81,6 +85,9 @@ struct PrefillArgs {
   const int* seq_slot;
   int nh, nkv, page_size, window;
   float scale_log2;              // scale * log2(e)
+  const float* sink;             // [nh] or null
+  const __nv_bfloat16* gate;     // [T, gate_stride], head h at h * out_hd; or null
+  int gate_stride, out_hd;
 };
 
 // Gathers keys kb*BK .. kb*BK+BK of one kv head (K and V) into a stage; rows past `last_key` are zeros.
@@ -255,15 +262,32 @@ attention_prefill_kernel(PrefillArgs a) {
     l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 1);
     l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 2);
   }
+  const float sink2 = a.sink ? a.sink[head] * 1.4426950408889634f : 0.f;
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
     if (!row_ok[h]) continue;
-    const float inv = 1.f / l_run[h];
-    __nv_bfloat16* dst = a.out + (size_t)(row0 + warp * 16 + g + 8 * h) * a.nh * HD + (size_t)head * HD;
+    float l = l_run[h], f = 1.f;
+    if (a.sink) {
+      // the sink as one more term of the denominator: exp2(sink2 - m) beside sum exp2(s - m)
+      const float m_fin = fmaxf(m_run[h], sink2);
+      f = exp2f(m_run[h] - m_fin);
+      l = l * f + exp2f(sink2 - m_fin);
+    }
+    const float inv = f / l;
+    const size_t r = (size_t)(row0 + warp * 16 + g + 8 * h);
+    __nv_bfloat16* dst = a.out + (r * a.nh + head) * a.out_hd;
+    const __nv_bfloat16* gt = a.gate ? a.gate + r * a.gate_stride + (size_t)head * a.out_hd : nullptr;
 #pragma unroll
     for (int i = 0; i < NT_O; ++i) {
-      const uint32_t v = pack_bf16(o[i][2 * h] * inv, o[i][2 * h + 1] * inv);
-      *reinterpret_cast<uint32_t*>(dst + i * 8 + 2 * t) = v;
+      const int d = i * 8 + 2 * t;
+      if (d >= a.out_hd) continue;
+      float y0 = o[i][2 * h] * inv, y1 = o[i][2 * h + 1] * inv;
+      if (gt) {
+        const float2 gg = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(gt + d));
+        y0 = __fdividef(y0, 1.f + __expf(-gg.x));
+        y1 = __fdividef(y1, 1.f + __expf(-gg.y));
+      }
+      *reinterpret_cast<uint32_t*>(dst + d) = pack_bf16(y0, y1);
     }
   }
 }
@@ -275,7 +299,9 @@ MI_API int mi_attention_head_dim() { return HD; }
 MI_API int mi_attention_prefill_bf16(void* out, const void* q_base, int q_stride, const void* kv_layer,
                                      const int* block_table, int bt_stride, const int* tiles, int n_tiles,
                                      const int* q_start, const int* q_len, const int* ctx_len, const int* seq_slot,
-                                     int nh, int nkv, int page_size, float scale, int window, cudaStream_t stream) {
+                                     int nh, int nkv, int page_size, float scale, int window, const float* sink,
+                                     const void* gate, int gate_stride, int out_hd, cudaStream_t stream) {
+  MI_REQUIRE(out_hd > 0 && out_hd <= HD && out_hd % 2 == 0 && gate_stride % 2 == 0, "attention_prefill: out_hd=%d must be even, up to %d", out_hd, HD);
   MI_REQUIRE(n_tiles >= 0 && nh > 0 && nkv > 0 && nh % nkv == 0, "attention_prefill: bad head counts nh=%d nkv=%d", nh, nkv);
   MI_REQUIRE(page_size > 0 && q_stride % 8 == 0, "attention_prefill: bad page_size=%d or q_stride=%d", page_size, q_stride);
   MI_REQUIRE(nh <= 65535, "attention_prefill: too many heads for one launch");
@@ -291,6 +317,7 @@ MI_API int mi_attention_prefill_bf16(void* out, const void* q_base, int q_stride
   a.q_start = q_start; a.q_len = q_len; a.ctx_len = ctx_len; a.seq_slot = seq_slot;
   a.nh = nh; a.nkv = nkv; a.page_size = page_size; a.window = window;
   a.scale_log2 = scale * 1.4426950408889634f;
+  a.sink = sink; a.gate = (const __nv_bfloat16*)gate; a.gate_stride = gate_stride; a.out_hd = out_hd;
   const size_t smem = (size_t)(BQ + 4 * BK) * LDS * sizeof(__nv_bfloat16);
   static bool configured = false;
   if (!configured) {

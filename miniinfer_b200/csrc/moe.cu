@@ -1,0 +1,455 @@
+// Routed experts (a mixture of small SwiGLU feed-forward layers of which each token uses `top`), in
+// five kernels and without a word read back by the host, so that a step can be recorded as a graph:
+//
+//   route    one warp per token: logits z = W_router h in float32 (W_router is kept in float32), scores
+//            s = sigmoid(z), choice = s + correction; the `top` experts of largest choice (ties: the lower
+//            index); weights = their s divided by (the sum of those s + 1e-20).
+//   align    one block: counts the (token, choice) pairs of every expert, gives each expert a range of
+//            rows rounded up to the row tile, and every pair a row in its expert's range.  Rows nobody
+//            owns are marked -1, tiles nobody owns too; the grid of the products is sized for the worst case.
+//   gate-up  grouped product: a block takes one row tile (rows of ONE expert, gathered from the tokens'
+//            normalised rows) and a slice of that expert's gate and up rows, and writes silu(g) * u.
+//   down     grouped product of those rows with the expert's down matrix, written as float32.
+//   combine  out[token] = sum over its choices, in the order of the choices, of weight * down row.
+//
+// A pair's products depend on its own row and its expert's weights only (sums over k in a fixed order), and a
+// token's sum runs over its choices in order, so a token's output does not depend on the rest of the batch.
+// bfloat16: mma.m16n8k16 with float32 accumulation, tiles through shared memory by cp.async in two
+// stages; float32: plain FMA in the order of k.
+#include "common.cuh"
+
+namespace {
+
+constexpr int MAX_EXPERTS = 256;
+constexpr int ROUTE_WARPS = 4;
+
+template <typename T>
+__global__ void __launch_bounds__(ROUTE_WARPS * 32)
+moe_route_kernel(const T* __restrict__ x, int Tn, int H, const float* __restrict__ wr, const float* __restrict__ corr,
+                 int E, int top, int* __restrict__ idx_out, float* __restrict__ w_out) {
+  __shared__ float s_score[ROUTE_WARPS][MAX_EXPERTS];
+  __shared__ float s_choice[ROUTE_WARPS][MAX_EXPERTS];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int t = blockIdx.x * ROUTE_WARPS + warp;
+  mi::grid_dependency_sync();
+  if (t >= Tn) return;
+  const T* row = x + (size_t)t * H;
+  for (int e = 0; e < E; ++e) {
+    const float* w = wr + (size_t)e * H;
+    float acc = 0.f;
+    for (int h = lane; h < H; h += 32) acc = fmaf(w[h], mi::to_float(row[h]), acc);
+    acc = mi::warp_sum(acc);
+    if (lane == 0) {
+      const float s = 1.f / (1.f + expf(-acc));
+      s_score[warp][e] = s;
+      s_choice[warp][e] = s + corr[e];
+    }
+  }
+  __syncwarp();
+  float sum = 0.f;
+  float mine = 0.f;   // lane k keeps the score of choice k
+  for (int k = 0; k < top; ++k) {
+    float best = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int e = lane; e < E; e += 32) {
+      const float c = s_choice[warp][e];
+      if (c > best) { best = c; bi = e; }     // within a lane indices grow, so the first of equals stays
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (ob > best || (ob == best && oi < bi)) { best = ob; bi = oi; }
+    }
+    const float s = s_score[warp][bi];
+    sum += s;
+    if (lane == k) mine = s;
+    if (lane == 0) {
+      idx_out[(size_t)t * top + k] = bi;
+      s_choice[warp][bi] = -INFINITY;
+    }
+    __syncwarp();
+  }
+  if (lane < top) w_out[(size_t)t * top + lane] = mine / (sum + 1e-20f);
+}
+
+__global__ void __launch_bounds__(1024)
+moe_align_kernel(const int* __restrict__ topk_idx, int n_pairs, int E, int TM, int* __restrict__ sorted_pair,
+                 int* __restrict__ pos_of, int* __restrict__ tile_expert, int max_rows, int max_tiles) {
+  __shared__ int count[MAX_EXPERTS];
+  __shared__ int start[MAX_EXPERTS + 1];
+  mi::grid_dependency_sync();
+  for (int e = threadIdx.x; e < E; e += blockDim.x) count[e] = 0;
+  for (int i = threadIdx.x; i < max_rows; i += blockDim.x) sorted_pair[i] = -1;
+  for (int i = threadIdx.x; i < max_tiles; i += blockDim.x) tile_expert[i] = -1;
+  __syncthreads();
+  for (int i = threadIdx.x; i < n_pairs; i += blockDim.x) atomicAdd(&count[topk_idx[i]], 1);
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int at = 0;
+    for (int e = 0; e < E; ++e) {
+      start[e] = at;
+      at += (count[e] + TM - 1) / TM * TM;
+    }
+    start[E] = at;
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < E; e += blockDim.x)
+    for (int tile = start[e] / TM; tile < start[e + 1] / TM; ++tile) tile_expert[tile] = e;
+  // rows inside an expert's range are handed out in the order of the pairs, so the layout is the same every time
+  for (int e = threadIdx.x; e < E; e += blockDim.x) {
+    if (count[e] == 0) continue;
+    int at = start[e];
+    for (int i = 0; i < n_pairs; ++i)
+      if (topk_idx[i] == e) { sorted_pair[at] = i; pos_of[i] = at; ++at; }
+  }
+}
+
+// the same without the serial walk, for steps with many pairs: a pair's row inside its expert's range comes from
+// an atomic counter (which row a pair gets then varies from run to run; its values do not depend on the row)
+__global__ void __launch_bounds__(1024)
+moe_align_atomic_kernel(const int* __restrict__ topk_idx, int n_pairs, int E, int TM, int* __restrict__ sorted_pair,
+                        int* __restrict__ pos_of, int* __restrict__ tile_expert, int max_rows, int max_tiles) {
+  __shared__ int count[MAX_EXPERTS];
+  __shared__ int start[MAX_EXPERTS + 1];
+  __shared__ int cursor[MAX_EXPERTS];
+  mi::grid_dependency_sync();
+  for (int e = threadIdx.x; e < E; e += blockDim.x) { count[e] = 0; cursor[e] = 0; }
+  for (int i = threadIdx.x; i < max_rows; i += blockDim.x) sorted_pair[i] = -1;
+  for (int i = threadIdx.x; i < max_tiles; i += blockDim.x) tile_expert[i] = -1;
+  __syncthreads();
+  for (int i = threadIdx.x; i < n_pairs; i += blockDim.x) atomicAdd(&count[topk_idx[i]], 1);
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int at = 0;
+    for (int e = 0; e < E; ++e) {
+      start[e] = at;
+      at += (count[e] + TM - 1) / TM * TM;
+    }
+    start[E] = at;
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < E; e += blockDim.x)
+    for (int tile = start[e] / TM; tile < start[e + 1] / TM; ++tile) tile_expert[tile] = e;
+  for (int i = threadIdx.x; i < n_pairs; i += blockDim.x) {
+    const int e = topk_idx[i];
+    const int at = start[e] + atomicAdd(&cursor[e], 1);
+    sorted_pair[at] = i;
+    pos_of[i] = at;
+  }
+}
+
+// ---------------------------------------------------------------------------------------------- products
+
+struct GroupedArgs {
+  const void* a;          // rows: gathered by pair (row = pair / top) if gather, else row = position
+  int a_stride;
+  const void* w;          // [E, n_rows_per_expert, K]
+  void* out;              // [max_rows, N]
+  const int* sorted_pair;
+  const int* tile_expert;
+  int N, K, top, gather;
+  long long w_expert_stride;   // elements between two experts' matrices
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void cp_async16(void* dst, const void* src, bool valid) {
+  const int n = valid ? 16 : 0;
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(dst)), "l"(src), "r"(n));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N)); }
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* p) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_u32(p)));
+}
+__device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+constexpr int GBK = 64;          // k per stage
+constexpr int GLDS = GBK + 8;    // shared-memory row stride in elements (odd number of 16-byte units)
+constexpr int WN_COLS = 32;      // columns of a warp's tile
+
+// WM x WN warps; a warp owns 16 rows x 32 columns (of gate and of up, if SWIGLU).  Block tile: 16 WM rows x 32 WN columns.
+template <int WM, int WN, bool SWIGLU>
+__global__ void __launch_bounds__(WM * WN * 32)
+moe_gemm_bf16_kernel(GroupedArgs a) {
+  constexpr int TM = 16 * WM, BN = WN_COLS * WN, THREADS = WM * WN * 32;
+  constexpr int NB = SWIGLU ? 2 : 1;
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  __nv_bfloat16* as = reinterpret_cast<__nv_bfloat16*>(smem_raw);        // [2][TM][GLDS]
+  __nv_bfloat16* bs = as + 2 * TM * GLDS;                                // [2][NB][BN][GLDS]
+  __shared__ int s_row[TM];
+  const int tile = blockIdx.y, n0 = blockIdx.x * BN;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int wm = warp % WM, wn = warp / WM;
+  const int g = lane >> 2, t = lane & 3, lm = lane >> 3, lr = lane & 7;
+  mi::grid_dependency_sync();
+  const int e = a.tile_expert[tile];
+  if (e < 0) return;
+  for (int r = threadIdx.x; r < TM; r += THREADS) {
+    const int pair = a.sorted_pair[tile * TM + r];
+    s_row[r] = pair < 0 ? -1 : (a.gather ? pair / a.top : tile * TM + r);
+  }
+  __syncthreads();
+  const __nv_bfloat16* A = (const __nv_bfloat16*)a.a;
+  const __nv_bfloat16* W = (const __nv_bfloat16*)a.w + (size_t)e * a.w_expert_stride;
+  const int K = a.K, N = a.N;
+  constexpr int CH = GBK / 8;   // 16-byte chunks of a staged row
+
+  auto load = [&](int stage, int k0) {
+    __nv_bfloat16* ad = as + stage * TM * GLDS;
+    for (int idx = threadIdx.x; idx < TM * CH; idx += THREADS) {
+      const int r = idx / CH, c = idx % CH;
+      const int row = s_row[r];
+      const bool valid = row >= 0 && k0 + c * 8 < K;
+      cp_async16(ad + r * GLDS + c * 8, valid ? A + (size_t)row * a.a_stride + k0 + c * 8 : A, valid);
+    }
+#pragma unroll
+    for (int b = 0; b < NB; ++b) {
+      __nv_bfloat16* bd = bs + (stage * NB + b) * BN * GLDS;
+      for (int idx = threadIdx.x; idx < BN * CH; idx += THREADS) {
+        const int r = idx / CH, c = idx % CH;
+        const bool valid = n0 + r < N && k0 + c * 8 < K;
+        cp_async16(bd + r * GLDS + c * 8, valid ? W + ((size_t)b * N + n0 + r) * K + k0 + c * 8 : W, valid);
+      }
+    }
+  };
+
+  float acc[NB][4][4];
+#pragma unroll
+  for (int b = 0; b < NB; ++b)
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int c = 0; c < 4; ++c) acc[b][i][c] = 0.f;
+
+  const int nk = (K + GBK - 1) / GBK;
+  load(0, 0);
+  cp_async_commit();
+  for (int kb = 0; kb < nk; ++kb) {
+    const int stage = kb & 1;
+    if (kb + 1 < nk) {
+      load(stage ^ 1, (kb + 1) * GBK);
+      cp_async_commit();
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
+    }
+    __syncthreads();
+    const __nv_bfloat16* at = as + stage * TM * GLDS + (wm * 16 + (lm & 1) * 8 + lr) * GLDS + (lm >> 1) * 8;
+#pragma unroll
+    for (int k = 0; k < GBK / 16; ++k) {
+      uint32_t af[4];
+      ldmatrix_x4(af, at + k * 16);
+#pragma unroll
+      for (int b = 0; b < NB; ++b) {
+        const __nv_bfloat16* bt = bs + (stage * NB + b) * BN * GLDS + (wn * WN_COLS + (lm >> 1) * 8 + lr) * GLDS + k * 16 + (lm & 1) * 8;
+#pragma unroll
+        for (int nb = 0; nb < 2; ++nb) {
+          uint32_t bf[4];
+          ldmatrix_x4(bf, bt + nb * 16 * GLDS);
+          mma_bf16(acc[b][2 * nb], af, bf[0], bf[1]);
+          mma_bf16(acc[b][2 * nb + 1], af, bf[2], bf[3]);
+        }
+      }
+    }
+    __syncthreads();
+  }
+
+  // rows g and g + 8 of the warp's 16, columns wn * 32 + i * 8 + 2 t (+1)
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const int r = wm * 16 + g + 8 * h;
+    if (s_row[r] < 0) continue;
+    const size_t orow = (size_t)(tile * TM + r) * N;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int n = n0 + wn * WN_COLS + i * 8 + 2 * t;
+      if (n >= N) continue;
+      if (SWIGLU) {
+        const float y0 = mi::silu_mul_fast(acc[0][i][2 * h], acc[1][i][2 * h]);
+        const float y1 = mi::silu_mul_fast(acc[0][i][2 * h + 1], acc[1][i][2 * h + 1]);
+        __nv_bfloat16* o = (__nv_bfloat16*)a.out + orow + n;
+        o[0] = __float2bfloat16_rn(y0);
+        if (n + 1 < N) o[1] = __float2bfloat16_rn(y1);
+      } else {
+        float* o = (float*)a.out + orow + n;
+        o[0] = acc[0][i][2 * h];
+        if (n + 1 < N) o[1] = acc[0][i][2 * h + 1];
+      }
+    }
+  }
+}
+
+// float32: 16 rows x 64 columns per block of 256 threads, a thread one row x 4 columns; sums in the order of k
+constexpr int FTM = 16, FBN = 64, FBK = 16;
+
+template <bool SWIGLU>
+__global__ void __launch_bounds__(256)
+moe_gemm_f32_kernel(GroupedArgs a) {
+  constexpr int NB = SWIGLU ? 2 : 1;
+  __shared__ float as[FTM][FBK + 1];
+  __shared__ float bs[NB][FBN][FBK + 1];
+  __shared__ int s_row[FTM];
+  const int tile = blockIdx.y, n0 = blockIdx.x * FBN;
+  mi::grid_dependency_sync();
+  const int e = a.tile_expert[tile];
+  if (e < 0) return;
+  if (threadIdx.x < FTM) {
+    const int pair = a.sorted_pair[tile * FTM + threadIdx.x];
+    s_row[threadIdx.x] = pair < 0 ? -1 : (a.gather ? pair / a.top : tile * FTM + (int)threadIdx.x);
+  }
+  __syncthreads();
+  const float* A = (const float*)a.a;
+  const float* W = (const float*)a.w + (size_t)e * a.w_expert_stride;
+  const int K = a.K, N = a.N;
+  const int r = threadIdx.x / 16, cg = threadIdx.x % 16;
+  float acc[NB][4];
+#pragma unroll
+  for (int b = 0; b < NB; ++b)
+#pragma unroll
+    for (int c = 0; c < 4; ++c) acc[b][c] = 0.f;
+  for (int k0 = 0; k0 < K; k0 += FBK) {
+    {
+      const int rr = threadIdx.x / FBK, kk = threadIdx.x % FBK;     // 16 x 16 = 256 values of A
+      const int row = s_row[rr];
+      as[rr][kk] = (row >= 0 && k0 + kk < K) ? A[(size_t)row * a.a_stride + k0 + kk] : 0.f;
+    }
+#pragma unroll
+    for (int b = 0; b < NB; ++b)
+      for (int idx = threadIdx.x; idx < FBN * FBK; idx += 256) {
+        const int rr = idx / FBK, kk = idx % FBK;
+        bs[b][rr][kk] = (n0 + rr < N && k0 + kk < K) ? W[((size_t)b * N + n0 + rr) * K + k0 + kk] : 0.f;
+      }
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < FBK; ++kk) {
+      const float av = as[r][kk];
+#pragma unroll
+      for (int b = 0; b < NB; ++b)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) acc[b][c] = fmaf(av, bs[b][cg * 4 + c][kk], acc[b][c]);
+    }
+    __syncthreads();
+  }
+  if (s_row[r] < 0) return;
+  float* o = (float*)a.out + (size_t)(tile * FTM + r) * N;
+#pragma unroll
+  for (int c = 0; c < 4; ++c) {
+    const int n = n0 + cg * 4 + c;
+    if (n < N) o[n] = SWIGLU ? mi::silu_mul_exact(acc[0][c], acc[NB - 1][c]) : acc[0][c];
+  }
+}
+
+template <typename TOut>
+__global__ void __launch_bounds__(256)
+moe_combine_kernel(TOut* __restrict__ out, const float* __restrict__ y, const int* __restrict__ pos_of,
+                   const float* __restrict__ w, int top, int N) {
+  mi::grid_dependency_sync();
+  const int t = blockIdx.x;
+  for (int n = threadIdx.x; n < N; n += blockDim.x) {
+    float acc = 0.f;
+    for (int k = 0; k < top; ++k) acc = fmaf(w[(size_t)t * top + k], y[(size_t)pos_of[(size_t)t * top + k] * N + n], acc);
+    out[(size_t)t * N + n] = mi::from_float<TOut>(acc);
+  }
+}
+
+template <int WM, int WN, bool SWIGLU>
+int launch_bf16(const GroupedArgs& a, int tiles, cudaStream_t stream) {
+  constexpr int TM = 16 * WM, BN = WN_COLS * WN;
+  const size_t smem = (size_t)(2 * TM + 2 * (SWIGLU ? 2 : 1) * BN) * GLDS * sizeof(__nv_bfloat16);
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(moe_gemm_bf16_kernel<WM, WN, SWIGLU>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return mi_fail("moe_gemm: cannot get %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
+    configured = true;
+  }
+  mi::launch(moe_gemm_bf16_kernel<WM, WN, SWIGLU>, dim3((a.N + BN - 1) / BN, tiles), dim3(WM * WN * 32), smem, stream, a);
+  return 0;
+}
+
+}  // namespace
+
+// Rows of a row tile for a step with `n_pairs` (token, choice) pairs: 16 while an expert gets few rows, 64 beyond.
+MI_API int mi_moe_row_tile(int n_pairs, int E, int dtype) {
+  if (dtype == MI_F32) return FTM;
+  return n_pairs >= 32 * E ? 64 : 16;
+}
+
+MI_API int mi_moe_route(const void* x, int dtype, int T, int H, const float* router, const float* correction, int E, int top,
+                        int* idx_out, float* w_out, cudaStream_t stream) {
+  MI_REQUIRE(T >= 0 && H > 0 && E > 0 && E <= MAX_EXPERTS, "moe_route: experts=%d must lie in 1..%d", E, MAX_EXPERTS);
+  MI_REQUIRE(top > 0 && top <= E && top <= 32, "moe_route: top=%d must lie in 1..min(experts, 32)", top);
+  if (T == 0) return 0;
+  const dim3 grid((T + ROUTE_WARPS - 1) / ROUTE_WARPS);
+  if (dtype == MI_BF16)
+    mi::launch(moe_route_kernel<__nv_bfloat16>, grid, dim3(ROUTE_WARPS * 32), 0, stream, (const __nv_bfloat16*)x, T, H, router, correction, E, top, idx_out, w_out);
+  else if (dtype == MI_F32)
+    mi::launch(moe_route_kernel<float>, grid, dim3(ROUTE_WARPS * 32), 0, stream, (const float*)x, T, H, router, correction, E, top, idx_out, w_out);
+  else
+    return mi_fail("moe_route: unknown dtype %d", dtype);
+  MI_LAUNCH_OK("moe_route");
+  return 0;
+}
+
+MI_API int mi_moe_align(const int* topk_idx, int n_pairs, int E, int TM, int* sorted_pair, int* pos_of, int* tile_expert,
+                        int max_rows, int max_tiles, cudaStream_t stream) {
+  MI_REQUIRE(E > 0 && E <= MAX_EXPERTS && TM > 0 && max_rows == max_tiles * TM, "moe_align: bad sizes");
+  MI_REQUIRE(max_rows >= n_pairs + E * (TM - 1), "moe_align: %d rows cannot hold %d pairs of %d experts in tiles of %d", max_rows, n_pairs, E, TM);
+  if (n_pairs == 0) return 0;
+  if (n_pairs <= 256)
+    mi::launch(moe_align_kernel, dim3(1), dim3(1024), 0, stream, topk_idx, n_pairs, E, TM, sorted_pair, pos_of, tile_expert, max_rows, max_tiles);
+  else
+    mi::launch(moe_align_atomic_kernel, dim3(1), dim3(1024), 0, stream, topk_idx, n_pairs, E, TM, sorted_pair, pos_of, tile_expert, max_rows, max_tiles);
+  MI_LAUNCH_OK("moe_align");
+  return 0;
+}
+
+// swiglu 1: out[row, :N] = silu(a w_gate^T) * (a w_up^T), the expert's matrix holding N gate rows and then N up rows,
+// rows gathered from the tokens; swiglu 0: out[row, :N] = a w^T in float32, rows by position.
+MI_API int mi_moe_gemm(const void* a_rows, int dtype, int a_stride, const void* w, void* out, const int* sorted_pair,
+                       const int* tile_expert, int max_tiles, int TM, int N, int K, int top, int swiglu, cudaStream_t stream) {
+  MI_REQUIRE(N > 0 && K > 0 && max_tiles >= 0 && max_tiles <= 65535, "moe_gemm: bad sizes N=%d K=%d tiles=%d", N, K, max_tiles);
+  if (max_tiles == 0) return 0;
+  GroupedArgs g;
+  g.a = a_rows; g.a_stride = a_stride; g.w = w; g.out = out; g.sorted_pair = sorted_pair; g.tile_expert = tile_expert;
+  g.N = N; g.K = K; g.top = top; g.gather = swiglu ? 1 : 0;
+  g.w_expert_stride = (long long)(swiglu ? 2 : 1) * N * K;
+  if (dtype == MI_F32) {
+    MI_REQUIRE(TM == FTM, "moe_gemm: the float32 product takes row tiles of %d", FTM);
+    const dim3 grid((N + FBN - 1) / FBN, max_tiles);
+    if (swiglu) mi::launch(moe_gemm_f32_kernel<true>, grid, dim3(256), 0, stream, g);
+    else mi::launch(moe_gemm_f32_kernel<false>, grid, dim3(256), 0, stream, g);
+  } else if (dtype == MI_BF16) {
+    MI_REQUIRE(K % 8 == 0 && a_stride % 8 == 0, "moe_gemm: K=%d and the row stride %d must be multiples of 8 in bfloat16", K, a_stride);
+    MI_REQUIRE(((uintptr_t)a_rows % 16) == 0 && ((uintptr_t)w % 16) == 0, "moe_gemm: operands must be 16-byte aligned");
+    int rc;
+    if (TM == 64) rc = swiglu ? launch_bf16<4, 2, true>(g, max_tiles, stream) : launch_bf16<4, 2, false>(g, max_tiles, stream);
+    else if (TM == 16) rc = swiglu ? launch_bf16<1, 4, true>(g, max_tiles, stream) : launch_bf16<1, 4, false>(g, max_tiles, stream);
+    else return mi_fail("moe_gemm: row tiles of 16 or 64 in bfloat16, got %d", TM);
+    if (rc) return rc;
+  } else {
+    return mi_fail("moe_gemm: unknown dtype %d", dtype);
+  }
+  MI_LAUNCH_OK("moe_gemm");
+  return 0;
+}
+
+MI_API int mi_moe_combine(void* out, int out_dtype, const float* y, const int* pos_of, const float* weights, int T, int top, int N,
+                          cudaStream_t stream) {
+  MI_REQUIRE(T >= 0 && top > 0 && N > 0, "moe_combine: bad sizes");
+  if (T == 0) return 0;
+  if (out_dtype == MI_BF16)
+    mi::launch(moe_combine_kernel<__nv_bfloat16>, dim3(T), dim3(256), 0, stream, (__nv_bfloat16*)out, y, pos_of, weights, top, N);
+  else if (out_dtype == MI_F32)
+    mi::launch(moe_combine_kernel<float>, dim3(T), dim3(256), 0, stream, (float*)out, y, pos_of, weights, top, N);
+  else
+    return mi_fail("moe_combine: unknown dtype %d", out_dtype);
+  MI_LAUNCH_OK("moe_combine");
+  return 0;
+}

@@ -129,3 +129,72 @@ MI_API int mi_add_rmsnorm(void* out, int out_dtype, float* resid, const void* de
   MI_LAUNCH_OK("add_rmsnorm");
   return 0;
 }
+
+// ------------------------------------------------------------------------------------------------
+// Layer norm (mean and variance, weight and bias) with the residual add in front of it.
+//
+//   sum[r, :] = resid[row(r), :] + (d1[row(r), :] + d2[row(r), :])      float32; d1, d2 optional
+//   out[r, :] = (sum - mean) * rsqrt(mean((sum - mean)^2) + eps) * w + b   rounded once to the output type
+//   resid[row(r), :] = sum                                                 if write_back
+//
+// Two deltas because a layer whose mixer and feed-forward read the same normalised rows leaves two
+// outputs to be added.  The row is kept in shared memory between the passes; the variance is the mean
+// of the squared deviations (second pass), not E[x^2] - mean^2.
+namespace {
+
+template <typename TOut, typename TDelta>
+__global__ void add_layernorm_kernel(TOut* __restrict__ out, float* __restrict__ resid,
+                                     const TDelta* __restrict__ d1, const TDelta* __restrict__ d2,
+                                     const float* __restrict__ w, const float* __restrict__ b,
+                                     const int* __restrict__ rows, int H, float eps, int write_back) {
+  extern __shared__ float ln_row[];
+  __shared__ float scratch[33];
+  const int r = blockIdx.x;
+  const int row = rows ? rows[r] : r;
+  mi::grid_dependency_sync();
+  float* x = resid + (size_t)row * H;
+  const TDelta* a = d1 ? d1 + (size_t)row * H : nullptr;
+  const TDelta* c = d2 ? d2 + (size_t)row * H : nullptr;
+  float s = 0.f;
+  for (int h = threadIdx.x; h < H; h += blockDim.x) {
+    float v = x[h];
+    if (a && c) v += mi::to_float(a[h]) + mi::to_float(c[h]);
+    else if (a) v += mi::to_float(a[h]);
+    else if (c) v += mi::to_float(c[h]);
+    if (write_back && (a || c)) x[h] = v;
+    ln_row[h] = v;
+    s += v;
+  }
+  const float mean = mi::block_sum(s, scratch) / (float)H;
+  float q = 0.f;
+  for (int h = threadIdx.x; h < H; h += blockDim.x) {
+    const float dv = ln_row[h] - mean;
+    q += dv * dv;
+  }
+  const float rstd = 1.f / sqrtf(mi::block_sum(q, scratch) / (float)H + eps);
+  TOut* o = out + (size_t)r * H;
+  for (int h = threadIdx.x; h < H; h += blockDim.x)
+    o[h] = mi::from_float<TOut>((ln_row[h] - mean) * rstd * w[h] + b[h]);
+}
+
+}  // namespace
+
+MI_API int mi_add_layernorm(void* out, int out_dtype, float* resid, const void* d1, const void* d2, int delta_dtype,
+                            const float* w, const float* b, const int* rows, int R, int H, float eps, int write_back,
+                            cudaStream_t stream) {
+  MI_REQUIRE(R >= 0 && H > 0 && H <= 12000, "layernorm: bad sizes R=%d H=%d (H up to 12000)", R, H);
+  MI_REQUIRE(eps > 0.f, "layernorm: eps must be positive");
+  if (R == 0) return 0;
+  const int threads = 256;  // fixed: the order of the reductions must not depend on the batch
+  const size_t smem = (size_t)H * sizeof(float);
+#define MI_LN_LAUNCH(TO, TD) \
+  mi::launch(add_layernorm_kernel<TO, TD>, dim3(R), dim3(threads), smem, stream, (TO*)out, resid, (const TD*)d1, (const TD*)d2, w, b, rows, H, eps, write_back)
+  if (out_dtype == MI_BF16 && delta_dtype == MI_BF16) MI_LN_LAUNCH(__nv_bfloat16, __nv_bfloat16);
+  else if (out_dtype == MI_F32 && delta_dtype == MI_F32) MI_LN_LAUNCH(float, float);
+  else if (out_dtype == MI_BF16 && delta_dtype == MI_F32) MI_LN_LAUNCH(__nv_bfloat16, float);
+  else if (out_dtype == MI_F32 && delta_dtype == MI_BF16) MI_LN_LAUNCH(float, __nv_bfloat16);
+  else return mi_fail("layernorm: unknown dtypes out=%d delta=%d", out_dtype, delta_dtype);
+#undef MI_LN_LAUNCH
+  MI_LAUNCH_OK("add_layernorm");
+  return 0;
+}

@@ -1,0 +1,133 @@
+// From the rows of a fused query / key / value product to what attention reads, for mixers whose heads
+// are not rotated: one pass over a token's heads that
+//
+//   * divides each query and key head by its root mean square over the head, x / sqrt(mean(x^2) + eps),
+//     in float32 (optionally times a weight per dimension), and writes the query heads, padded with
+//     zeros to the cache's head size, into a packed buffer [token, head, cache head size];
+//   * mixes the token's value heads with the values another layer made for the same token,
+//     v <- (1 - lambda) v + lambda v_other (lambda read from the device), or records them as that
+//     other layer's values (v_mode 1), or leaves them alone (v_mode 0);
+//   * stores key and value heads into the layer's pages at slot_mapping[token] (page * page_size +
+//     offset), padded with zeros.  What is cached is the normalised key and the mixed value.
+//
+// Key heads have `dim` values and value heads `vdim`; the cache keeps both in rows of `hdp >= max(dim, vdim)`
+// values, so a zero tail adds nothing to a score and its output columns are dropped by the attention
+// kernels (out_hd).  A block per token, the token's heads dealt to its warps.
+#include "common.cuh"
+
+namespace {
+
+constexpr int PREP_WARPS = 4;
+constexpr int PREP_MAX_PER_LANE = 8;   // head sizes up to 256
+
+template <typename T>
+struct PrepArgs {
+  const T* proj;          // [tokens, proj_stride]: queries at q_off, keys at k_off, values at v_off
+  int proj_stride, q_off, k_off, v_off;
+  int nh, nkv, dim, vdim, hdp;
+  T* q_out;               // [tokens, nh * hdp]
+  const float* q_w;       // [dim] or null
+  const float* k_w;       // [dim] or null
+  float eps;
+  int normalise;          // 0: queries and keys pass unchanged
+  const float* lambda;    // device scalar (v_mode 2)
+  T* v_other;             // [tokens, nkv * vdim]: written (v_mode 1) or read (v_mode 2)
+  int v_mode;
+  const int* slot_mapping;  // null: nothing is stored
+  T* kv_layer;            // [page, 2, nkv, page_size, hdp]
+  int page_size;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(PREP_WARPS * 32)
+qkv_prepare_kernel(PrepArgs<T> a) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int tkn = blockIdx.x;
+  const float lam = (a.v_mode == 2) ? *a.lambda : 0.f;       // a weight: no kernel writes it
+  const int slot = a.slot_mapping ? a.slot_mapping[tkn] : -1;  // part of the step's description
+  mi::grid_dependency_sync();
+  const T* row = a.proj + (size_t)tkn * a.proj_stride;
+  const int units = a.nh + 2 * a.nkv;
+  const int page = slot >= 0 ? slot / a.page_size : 0, off = slot >= 0 ? slot % a.page_size : 0;
+  for (int u = warp; u < units; u += PREP_WARPS) {
+    if (u < a.nh + a.nkv) {
+      // a query head or a key head
+      const bool is_q = u < a.nh;
+      const int h = is_q ? u : u - a.nh;
+      const T* src = row + (is_q ? a.q_off : a.k_off) + (size_t)h * a.dim;
+      const float* w = is_q ? a.q_w : a.k_w;
+      float v[PREP_MAX_PER_LANE];
+      float ss = 0.f;
+#pragma unroll
+      for (int i = 0; i < PREP_MAX_PER_LANE; ++i) {
+        const int d = lane + 32 * i;
+        v[i] = d < a.dim ? mi::to_float(src[d]) : 0.f;
+        ss += v[i] * v[i];
+      }
+      float r = 1.f;
+      if (a.normalise) r = 1.f / sqrtf(mi::warp_sum(ss) / (float)a.dim + a.eps);
+      T* dst = nullptr;
+      if (is_q) dst = a.q_out + ((size_t)tkn * a.nh + h) * a.hdp;
+      else if (slot >= 0) dst = a.kv_layer + ((((size_t)page * 2 + 0) * a.nkv + h) * a.page_size + off) * a.hdp;
+      if (dst) {
+#pragma unroll
+        for (int i = 0; i < PREP_MAX_PER_LANE; ++i) {
+          const int d = lane + 32 * i;
+          if (d < a.hdp) {
+            float y = v[i] * r;
+            if (w && d < a.dim) y *= w[d];
+            dst[d] = mi::from_float<T>(d < a.dim ? y : 0.f);
+          }
+        }
+      }
+    } else {
+      // a value head
+      const int h = u - a.nh - a.nkv;
+      const T* src = row + a.v_off + (size_t)h * a.vdim;
+      T* other = a.v_other ? a.v_other + ((size_t)tkn * a.nkv + h) * a.vdim : nullptr;
+      T* dst = slot >= 0 ? a.kv_layer + ((((size_t)page * 2 + 1) * a.nkv + h) * a.page_size + off) * a.hdp : nullptr;
+#pragma unroll
+      for (int i = 0; i < PREP_MAX_PER_LANE; ++i) {
+        const int d = lane + 32 * i;
+        if (d >= a.hdp) continue;
+        float y = 0.f;
+        if (d < a.vdim) {
+          y = mi::to_float(src[d]);
+          if (a.v_mode == 1) other[d] = mi::from_float<T>(y);
+          else if (a.v_mode == 2) y = (1.f - lam) * y + lam * mi::to_float(other[d]);
+        }
+        if (dst) dst[d] = mi::from_float<T>(y);
+      }
+    }
+  }
+}
+
+}  // namespace
+
+MI_API int mi_qkv_norm_mix_store(const void* proj, int dtype, int proj_stride, int q_off, int k_off, int v_off, int T, int nh,
+                                 int nkv, int dim, int vdim, int hdp, void* q_out, const float* q_w, const float* k_w,
+                                 float eps, int normalise, const float* lambda, void* v_other, int v_mode,
+                                 const int* slot_mapping, void* kv_layer, int page_size, cudaStream_t stream) {
+  MI_REQUIRE(T >= 0 && nh > 0 && nkv > 0 && dim > 0 && vdim > 0, "qkv_prepare: bad sizes");
+  MI_REQUIRE(hdp >= dim && hdp >= vdim && hdp <= 32 * PREP_MAX_PER_LANE, "qkv_prepare: cache head size %d must cover dim=%d and vdim=%d, up to %d",
+             hdp, dim, vdim, 32 * PREP_MAX_PER_LANE);
+  MI_REQUIRE(v_mode >= 0 && v_mode <= 2 && (v_mode == 0 || v_other != nullptr) && (v_mode != 2 || lambda != nullptr),
+             "qkv_prepare: value mixing needs the other layer's values and lambda");
+  MI_REQUIRE(slot_mapping == nullptr || (kv_layer != nullptr && page_size > 0), "qkv_prepare: a store needs the cache layer");
+  if (T == 0) return 0;
+#define MI_PREP(TT)                                                                                          \
+  do {                                                                                                       \
+    PrepArgs<TT> a;                                                                                          \
+    a.proj = (const TT*)proj; a.proj_stride = proj_stride; a.q_off = q_off; a.k_off = k_off; a.v_off = v_off; \
+    a.nh = nh; a.nkv = nkv; a.dim = dim; a.vdim = vdim; a.hdp = hdp; a.q_out = (TT*)q_out; a.q_w = q_w; a.k_w = k_w; \
+    a.eps = eps; a.normalise = normalise; a.lambda = lambda; a.v_other = (TT*)v_other; a.v_mode = v_mode;     \
+    a.slot_mapping = slot_mapping; a.kv_layer = (TT*)kv_layer; a.page_size = page_size;                      \
+    mi::launch(qkv_prepare_kernel<TT>, dim3(T), dim3(PREP_WARPS * 32), 0, stream, a);                        \
+  } while (0)
+  if (dtype == MI_BF16) MI_PREP(__nv_bfloat16);
+  else if (dtype == MI_F32) MI_PREP(float);
+  else return mi_fail("qkv_prepare: unknown dtype %d", dtype);
+#undef MI_PREP
+  MI_LAUNCH_OK("qkv_prepare");
+  return 0;
+}

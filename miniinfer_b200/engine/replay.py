@@ -35,7 +35,7 @@ MAX_LIVE_REQUESTS = 8
 
 class TraceRunner:
   def __init__(self, model_dir: str, dtype, max_tokens: int, device: str = "cuda:0",
-               page_size: int = TRACE_PAGE_SIZE, num_pages: Optional[int] = None):
+               page_size: int = TRACE_PAGE_SIZE, num_pages: Optional[int] = None, max_requests: int = MAX_LIVE_REQUESTS):
     self.dtype = parse_dtype(dtype)
     self.device = torch.device(device)
     if self.device.type == "cuda":
@@ -50,7 +50,7 @@ class TraceRunner:
     if num_pages is None:
       num_pages = max(1, -(-int(max_tokens) // page_size))
     max_len = min(self.model_config.max_position_embeddings, num_pages * page_size)
-    self.cache = KVCacheManager(self.spec.cache_layer_specs(), page_size, num_pages, MAX_LIVE_REQUESTS, max_len,
+    self.cache = KVCacheManager(self.spec.cache_layer_specs(), page_size, num_pages, max_requests, max_len,
                                 self.dtype, self.device)
     self.runner = ModelRunner(self.spec, self.cache, self.dtype, self.device)
 
@@ -88,12 +88,14 @@ def main(argv=None, stdin: Optional[IO[str]] = None, stdout: Optional[IO[str]] =
   p.add_argument("--page-size", type=int, default=TRACE_PAGE_SIZE, help="tokens per page of the cache (default 64)")
   p.add_argument("--num-pages", type=int, default=None,
                  help="pages of the cache pool (default: --max-tokens divided by the page size, rounded up)")
+  p.add_argument("--max-requests", type=int, default=4, help="request slots: the most requests that are live at a time (default 4)")
   p.add_argument("--device", default="cuda:0")
   args = p.parse_args(argv)
   stdin = stdin or sys.stdin
   stdout = stdout or sys.stdout
   os.makedirs(args.out, exist_ok=True)
-  tr = TraceRunner(args.model, args.dtype, args.max_tokens, args.device, page_size=args.page_size, num_pages=args.num_pages)
+  tr = TraceRunner(args.model, args.dtype, args.max_tokens, args.device, page_size=args.page_size, num_pages=args.num_pages,
+                   max_requests=args.max_requests)
   for line in stdin:
     line = line.strip()
     if not line:

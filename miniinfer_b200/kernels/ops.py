@@ -122,14 +122,37 @@ def _stream() -> ctypes.c_void_p:
 # --------------------------------------------------------------------------------------------
 
 
-def embedding(out: torch.Tensor, table: torch.Tensor, ids: torch.Tensor) -> None:
-  """out[t] = table[ids[t]] as float32.  ids: int32, already checked to lie in the vocabulary."""
+def embedding(out: torch.Tensor, table: torch.Tensor, ids: torch.Tensor, scale: float = 1.0) -> None:
+  """out[t] = scale * table[ids[t]] as float32.  ids: int32, already checked to lie in the vocabulary."""
   lib = common_lib()
   T, H = out.shape
   if table.shape[1] != H or ids.shape[0] != T:
     raise KernelError("embedding: shapes do not match")
   _check(lib, lib.mi_embedding(_ptr(out, torch.float32), _ptr(table), _dt(table), _ptr(ids, torch.int32),
-                               T, H, _stream()))
+                               T, H, ctypes.c_float(scale), _stream()))
+
+
+def add_layernorm(out: torch.Tensor, resid: torch.Tensor, delta: Optional[torch.Tensor], delta2: Optional[torch.Tensor],
+                  weight: torch.Tensor, bias: torch.Tensor, eps: float, rows: Optional[torch.Tensor] = None,
+                  write_back: bool = True) -> None:
+  """out[r] = (s - mean(s)) / sqrt(var(s) + eps) * weight + bias with s = resid[row] + (delta[row] + delta2[row]), both
+  deltas optional and of one dtype; the sum goes back to resid if write_back.  All in float32."""
+  lib = common_lib()
+  R, H = out.shape
+  if resid.shape[1] != H or weight.shape != (H,) or bias.shape != (H,):
+    raise KernelError("add_layernorm: shapes do not match")
+  for d in (delta, delta2):
+    if d is not None and d.shape != resid.shape:
+      raise KernelError("add_layernorm: a delta differs from the residual in shape")
+  if delta is not None and delta2 is not None and delta.dtype != delta2.dtype:
+    raise KernelError("add_layernorm: the two deltas differ in dtype")
+  if (rows is None and resid.shape[0] != R) or (rows is not None and rows.shape[0] != R):
+    raise KernelError("add_layernorm: out, rows and resid differ in rows")
+  first = delta if delta is not None else delta2
+  _check(lib, lib.mi_add_layernorm(_ptr(out), _dt(out), _ptr(resid, torch.float32), _ptr(delta), _ptr(delta2),
+                                   _dt(first) if first is not None else F32, _ptr(weight, torch.float32), _ptr(bias, torch.float32),
+                                   _ptr(rows, torch.int32) if rows is not None else _ptr(None), R, H,
+                                   ctypes.c_float(eps), int(bool(write_back)), _stream()))
 
 
 def add_rmsnorm(out: torch.Tensor, resid: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor,
@@ -356,6 +379,91 @@ def qk_norm_rope_store(qkv: torch.Tensor, q_weight: Optional[torch.Tensor], k_we
     _ptr(kv_layer), T, num_heads, num_kv_heads, head_dim, page_size, ctypes.c_float(eps), _stream()))
 
 
+def qkv_norm_mix_store(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, q_out: torch.Tensor, num_heads: int,
+                       num_kv_heads: int, dim: int, vdim: int, eps: float, normalise: bool = True,
+                       q_weight: Optional[torch.Tensor] = None, k_weight: Optional[torch.Tensor] = None,
+                       mix: Optional[torch.Tensor] = None, v_other: Optional[torch.Tensor] = None, v_mode: int = 0,
+                       slot_mapping: Optional[torch.Tensor] = None, kv_layer: Optional[torch.Tensor] = None) -> None:
+  """From the rows of a fused projection (queries at column ``q_off``, keys at ``k_off``, values at ``v_off``) to what
+  attention reads, for heads that are not rotated: query and key heads divided by their root mean square over
+  ``dim`` (x / sqrt(mean(x^2) + eps), float32; times ``q_weight`` / ``k_weight`` if given); queries into
+  ``q_out [tokens, heads, cache head size]`` padded with zeros; values mixed with another layer's values of the same
+  token (``v_mode`` 2: v <- (1 - mix) v + mix v_other, ``mix`` a scalar on the device), recorded as those values
+  (``v_mode`` 1) or left alone (0); keys and values stored into the layer's pages at ``slot_mapping``."""
+  lib = common_lib()
+  T = proj.shape[0]
+  hdp = q_out.shape[1] // num_heads
+  if q_out.shape != (T, num_heads * hdp) or q_out.dtype != proj.dtype:
+    raise KernelError("qkv_norm_mix_store: q_out does not match the projection rows")
+  width = proj.shape[1]
+  if max(q_off + num_heads * dim, k_off + num_kv_heads * dim, v_off + num_kv_heads * vdim) > width:
+    raise KernelError("qkv_norm_mix_store: the heads do not fit the projection rows")
+  page_size = 0
+  if kv_layer is not None:
+    if kv_layer.dtype != proj.dtype or kv_layer.dim() != 5 or kv_layer.shape[1:3] != (2, num_kv_heads) or kv_layer.shape[4] != hdp:
+      raise KernelError(f"qkv_norm_mix_store: cache layer has shape {tuple(kv_layer.shape)}, head size {hdp} expected")
+    page_size = kv_layer.shape[3]
+  if v_mode and (v_other is None or v_other.shape != (T, num_kv_heads * vdim) or v_other.dtype != proj.dtype):
+    raise KernelError("qkv_norm_mix_store: the other layer's values must be [tokens, kv heads * vdim] in the rows' dtype")
+  none = _ptr(None)
+  _check(lib, lib.mi_qkv_norm_mix_store(
+    _ptr(proj), _dt(proj), width, q_off, k_off, v_off, T, num_heads, num_kv_heads, dim, vdim, hdp, _ptr(q_out),
+    _ptr(q_weight, torch.float32) if q_weight is not None else none, _ptr(k_weight, torch.float32) if k_weight is not None else none,
+    ctypes.c_float(eps), int(bool(normalise)), _ptr(mix, torch.float32) if mix is not None else none,
+    _ptr(v_other) if v_other is not None else none, int(v_mode),
+    _ptr(slot_mapping, torch.int32) if (slot_mapping is not None and kv_layer is not None) else none,
+    _ptr(kv_layer) if kv_layer is not None else none, page_size, _stream()))
+
+
+def moe_row_tile(num_pairs: int, num_experts: int, dtype: torch.dtype) -> int:
+  """Rows of a row tile of the grouped products for a step with ``num_pairs`` (token, choice) pairs."""
+  return int(common_lib().mi_moe_row_tile(num_pairs, num_experts, F32 if dtype == torch.float32 else BF16))
+
+
+def moe_rows(num_pairs: int, num_experts: int, tile: int) -> int:
+  """Rows that hold ``num_pairs`` pairs when every expert's rows start at a multiple of ``tile``, in the worst case."""
+  return -(-(num_pairs + num_experts * (tile - 1)) // tile) * tile
+
+
+def routed_experts(out: torch.Tensor, x: torch.Tensor, router: torch.Tensor, correction: torch.Tensor, gate_up: torch.Tensor,
+                   down: torch.Tensor, top: int, workspace) -> None:
+  """out[t] = sum over the ``top`` chosen experts of weight * down_e(silu(gate_e x) * up_e x).
+
+  ``router [E, H]`` and ``correction [E]`` float32: scores sigmoid(router x) in float32; the ``top`` experts of largest
+  score + correction are chosen; weights are their scores divided by the scores' sum (+ 1e-20).  ``gate_up [E, 2 ff, H]``
+  (an expert's gate rows, then its up rows) and ``down [E, H, ff]`` in the rows' dtype.  Five launches, nothing read
+  back by the host; scratch from ``workspace``."""
+  lib = common_lib()
+  T, H = x.shape
+  E = router.shape[0]
+  ff = down.shape[2]
+  if router.shape != (E, H) or correction.shape != (E,) or gate_up.shape != (E, 2 * ff, H) or down.shape != (E, H, ff) or out.shape != (T, H):
+    raise KernelError(f"routed_experts: shapes do not match: x {tuple(x.shape)}, router {tuple(router.shape)}, "
+                      f"gate_up {tuple(gate_up.shape)}, down {tuple(down.shape)}")
+  if gate_up.dtype != x.dtype or down.dtype != x.dtype or out.dtype != x.dtype:
+    raise KernelError("routed_experts: rows, experts and out must share a dtype")
+  if T == 0:
+    return
+  pairs = T * top
+  tile = moe_row_tile(pairs, E, x.dtype)
+  rows = moe_rows(pairs, E, tile)
+  tiles = rows // tile
+  idx = workspace.buffer("moe_choice", (pairs,), torch.int32)
+  wts = workspace.buffer("moe_weight", (pairs,), torch.float32)
+  sorted_pair = workspace.buffer("moe_sorted", (rows,), torch.int32)
+  pos_of = workspace.buffer("moe_pos", (pairs,), torch.int32)
+  tile_expert = workspace.buffer("moe_tile_expert", (tiles,), torch.int32)
+  act = workspace.buffer("moe_act", (rows, ff), x.dtype)
+  y = workspace.buffer("moe_y", (rows, H), torch.float32)
+  dt, st = _dt(x), _stream()
+  _check(lib, lib.mi_moe_route(_ptr(x), dt, T, H, _ptr(router, torch.float32), _ptr(correction, torch.float32), E, top,
+                               _ptr(idx), _ptr(wts), st))
+  _check(lib, lib.mi_moe_align(_ptr(idx), pairs, E, tile, _ptr(sorted_pair), _ptr(pos_of), _ptr(tile_expert), rows, tiles, st))
+  _check(lib, lib.mi_moe_gemm(_ptr(x), dt, H, _ptr(gate_up), _ptr(act), _ptr(sorted_pair), _ptr(tile_expert), tiles, tile, ff, H, top, 1, st))
+  _check(lib, lib.mi_moe_gemm(_ptr(act), dt, ff, _ptr(down), _ptr(y), _ptr(sorted_pair), _ptr(tile_expert), tiles, tile, H, ff, top, 0, st))
+  _check(lib, lib.mi_moe_combine(_ptr(out), _dt(out), _ptr(y), _ptr(pos_of), _ptr(wts), T, top, H, st))
+
+
 def linear_swiglu(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, workspace, force_skinny: bool = False,
                   force_tc: bool = False, force_stream: bool = False) -> None:
   """out[M, I] = silu(x @ w[:I]^T) * (x @ w[I:]^T): the gate-and-up product of a SwiGLU feed-forward.
@@ -468,25 +576,61 @@ class AttentionBatch:
 
 def attention(out: torch.Tensor, qkv: torch.Tensor, kv_layer: torch.Tensor, block_table: torch.Tensor,
               batch: AttentionBatch, num_heads: int, num_kv_heads: int, head_dim: int, scale: float,
-              window: Optional[int], force_generic: bool = False) -> None:
+              window: Optional[int], force_generic: bool = False, sink: Optional[torch.Tensor] = None,
+              gate: Optional[torch.Tensor] = None, gate_offset: int = 0, out_hd: Optional[int] = None) -> None:
   """out[t, h*hd:(h+1)*hd] = softmax(scale * q . K^T over the keys the token may see) V, reading
-  K and V through the block table.  ``qkv`` holds the step's fused rows; q is its first part."""
+  K and V through the block table.  ``qkv`` holds the step's fused rows; q is its first part.
+
+  Options: ``sink [heads]`` float32 - a learned logit per query head whose exponential joins the softmax's denominator
+  once, unscaled, with no key and no value; ``gate`` - rows ``[tokens, width]`` whose columns from ``gate_offset`` on hold,
+  head after head, a gate for every output value: the output is multiplied with its sigmoid; ``out_hd`` - only the first
+  ``out_hd`` values of each head are written, ``out`` being ``[tokens, heads * out_hd]`` (cache rows padded to ``head_dim``)."""
   T = qkv.shape[0]
-  if out.shape != (T, num_heads * head_dim) or out.dtype != qkv.dtype or kv_layer.dtype != qkv.dtype:
+  ohd = head_dim if out_hd is None else int(out_hd)
+  if out.shape != (T, num_heads * ohd) or out.dtype != qkv.dtype or kv_layer.dtype != qkv.dtype or not (0 < ohd <= head_dim):
     raise KernelError("attention: shapes or dtypes do not match")
   page_size = kv_layer.shape[3]
   if kv_layer.shape[1:] != (2, num_kv_heads, page_size, head_dim):
     raise KernelError(f"attention: cache layer has shape {tuple(kv_layer.shape)}")
+  if sink is not None and (sink.shape != (num_heads,) or sink.dtype != torch.float32):
+    raise KernelError("attention: the sinks must be one float32 per query head")
+  gate_stride = 0
+  if gate is not None:
+    gate_stride = gate.shape[1]
+    if gate.dtype != qkv.dtype or gate.shape[0] != T or gate_offset + num_heads * ohd > gate_stride or not gate.is_contiguous():
+      raise KernelError("attention: the gate rows do not match")
+  opts = _AttentionOptions(sink, gate, gate_offset, gate_stride, ohd)
   win = int(window) if window else 0
-  if qkv.dtype == torch.bfloat16 and not force_generic and head_dim % 16 == 0 and 16 <= head_dim <= 256:
-    _attention_bf16(out, qkv, kv_layer, block_table, batch, num_heads, num_kv_heads, head_dim, scale, win, page_size)
+  even = ohd % 2 == 0 and gate_offset % 2 == 0 and gate_stride % 2 == 0
+  if qkv.dtype == torch.bfloat16 and not force_generic and head_dim % 16 == 0 and 16 <= head_dim <= 256 and even:
+    _attention_bf16(out, qkv, kv_layer, block_table, batch, num_heads, num_kv_heads, head_dim, scale, win, page_size, opts)
     return
   lib = common_lib()
   _check(lib, lib.mi_attention_generic(
     _ptr(out), _ptr(qkv), qkv.shape[1], _dt(qkv), _ptr(kv_layer), _ptr(block_table, torch.int32),
     block_table.shape[1], _ptr(batch.token_item, torch.int32), _ptr(batch.positions, torch.int32),
     _ptr(batch.seq_slot, torch.int32), T, num_heads, num_kv_heads, head_dim, page_size,
-    ctypes.c_float(scale), win, _stream()))
+    ctypes.c_float(scale), win, opts.sink_ptr(), opts.gate_ptr(), gate_stride, ohd, _stream()))
+
+
+class _AttentionOptions:
+  """The optional sink, output gate and output width of an attention call, as the kernels take them."""
+
+  __slots__ = ("sink", "gate", "gate_offset", "gate_stride", "out_hd")
+
+  def __init__(self, sink, gate, gate_offset, gate_stride, out_hd):
+    self.sink, self.gate, self.gate_offset, self.gate_stride, self.out_hd = sink, gate, gate_offset, gate_stride, out_hd
+
+  def plain(self, head_dim: int) -> bool:
+    return self.sink is None and self.gate is None and self.out_hd == head_dim
+
+  def sink_ptr(self):
+    return _ptr(self.sink, torch.float32) if self.sink is not None else _ptr(None)
+
+  def gate_ptr(self):
+    if self.gate is None:
+      return _ptr(None)
+    return ctypes.c_void_p(self.gate.data_ptr() + self.gate_offset * self.gate.element_size())
 
 
 def _rope_in_attention(qkv, cos_sin, kv_layer, batch, nh, nkv, hd, win, page_size) -> int:
@@ -595,12 +739,15 @@ def decode_cluster_size(lib, head_dim: int, num_decode: int, num_kv_heads: int, 
 DECODE_CLUSTER_MAX_TILES_PER_BLOCK = 64
 
 
-def _attention_bf16(out, qkv, kv_layer, block_table, batch, nh, nkv, hd, scale, win, page_size) -> None:
+def _attention_bf16(out, qkv, kv_layer, block_table, batch, nh, nkv, hd, scale, win, page_size, opts=None) -> None:
   """Tensor-core kernel for the items with several new tokens, split-KV kernel for the decode items;
   the two write disjoint rows of ``out``."""
   lib = attention_lib(hd)
+  if opts is None:
+    opts = _AttentionOptions(None, None, 0, 0, hd)
+  plain = opts.plain(hd)      # the TMA / tcgen05 kernels take neither sink nor gate nor a narrower output
   if batch.num_prefill_tiles:
-    use_tc = (page_size % 64 == 0 and lib.mi_attention_prefill_tc_supported() == 1
+    use_tc = (plain and page_size % 64 == 0 and lib.mi_attention_prefill_tc_supported() == 1
               and os.environ.get("MINIINFER_B200_PREFILL_TC", "1") != "0")
     if use_tc:
       if batch.scratch is not None:
@@ -625,11 +772,11 @@ def _attention_bf16(out, qkv, kv_layer, block_table, batch, nh, nkv, hd, scale, 
         _ptr(out), _ptr(qkv), qkv.shape[1], _ptr(kv_layer), _ptr(block_table, torch.int32), block_table.shape[1],
         _ptr(batch.prefill_tiles, torch.int32), batch.num_prefill_tiles, _ptr(batch.q_start, torch.int32),
         _ptr(batch.q_len, torch.int32), _ptr(batch.ctx_len, torch.int32), _ptr(batch.seq_slot, torch.int32),
-        nh, nkv, page_size, ctypes.c_float(scale), win, _stream()))
+        nh, nkv, page_size, ctypes.c_float(scale), win, opts.sink_ptr(), opts.gate_ptr(), opts.gate_stride, opts.out_hd, _stream()))
   if batch.num_decode:
     span = min(batch.max_ctx_len, win) if win else batch.max_ctx_len
     G = nh // nkv
-    tma_shapes = hd % 64 == 0 and page_size % 64 == 0 and os.environ.get("MINIINFER_B200_DECODE_TMA", "1") != "0"
+    tma_shapes = plain and hd % 64 == 0 and page_size % 64 == 0 and os.environ.get("MINIINFER_B200_DECODE_TMA", "1") != "0"
     cluster = decode_cluster_size(lib, hd, batch.num_decode, nkv, span) if (tma_shapes and G <= 8) else 0
     if cluster:
       if batch.scratch is not None:
@@ -646,7 +793,7 @@ def _attention_bf16(out, qkv, kv_layer, block_table, batch, nh, nkv, hd, scale, 
       return
     # more than 8 query heads per kv head: the TMA kernel would walk an item's tiles twice and hand a stage back only
     # in the second pass, which cannot work once an item has more tiles than there are stages - the cp.async kernel takes those
-    use_tma = (hd % 64 == 0 and page_size % 64 == 0 and G <= 8 and os.environ.get("MINIINFER_B200_DECODE_TMA", "1") != "0")
+    use_tma = (plain and hd % 64 == 0 and page_size % 64 == 0 and G <= 8 and os.environ.get("MINIINFER_B200_DECODE_TMA", "1") != "0")
     if use_tma:
       # the TMA kernel deals 64-key tiles out evenly; a (request, kv head) is cut into at most as many
       # pieces as it has tiles, and no more than there are blocks
@@ -675,7 +822,8 @@ def _attention_bf16(out, qkv, kv_layer, block_table, batch, nh, nkv, hd, scale, 
         _ptr(out), _ptr(qkv), qkv.shape[1], _ptr(kv_layer), _ptr(block_table, torch.int32), block_table.shape[1],
         _ptr(batch.decode_items, torch.int32), _ptr(batch.q_start, torch.int32), _ptr(batch.ctx_len, torch.int32),
         _ptr(batch.seq_slot, torch.int32), _ptr(scratch, torch.float32), _ptr(counters[1:], torch.int32),
-        batch.num_decode, nh, nkv, page_size, ctypes.c_float(scale), win, chunk, max_splits, _stream()))
+        batch.num_decode, nh, nkv, page_size, ctypes.c_float(scale), win, chunk, max_splits,
+        opts.sink_ptr(), opts.gate_ptr(), opts.gate_stride, opts.out_hd, _stream()))
 
 
 _tensor_maps: Dict[tuple, ctypes.Array] = {}

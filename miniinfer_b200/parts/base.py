@@ -6,7 +6,8 @@ layer it is, or what the other parts of its block are.
 
 Interfaces (see the concrete parts for examples):
 
-``Norm``           ``add_norm(resid, delta, ctx) -> x``: adds ``delta`` (or nothing) into the float32
+``Norm``           ``add_norm(resid, delta, ctx) -> x``: adds ``delta`` (a tensor, a pair of tensors that are
+                   both added, or nothing) into the float32
                    residual rows in place and returns the normalised rows in the compute dtype;
                    ``norm_rows(resid, delta, rows, ctx) -> x``: the same for selected rows, without
                    changing the residual.
@@ -46,15 +47,16 @@ class Piece:
 @dataclass
 class ParamSpec:
   """A parameter: its shape, its role (``matrix``/``table``: kept in the compute dtype; ``vector``:
-  kept in float32; ``int``: kept as int32) and the alternative sets of file tensors that fill it."""
+  kept in float32, scalars included; ``matrix_f32``: a matrix kept in float32 whatever the compute dtype, for what is
+  computed in 32-bit such as a router; ``int``: kept as int32) and the alternative sets of file tensors that fill it."""
 
   shape: Tuple[int, ...]
   role: str
   sources: List[List[Piece]]
-  init: str = "normal"            # random-weights mode: "normal" (std given by the model) or "ones_noise"
+  init: str = "normal"            # random-weights mode: "normal" (std given by the model), "ones_noise" (about 1) or "half_noise" (about 0.5)
 
   def __post_init__(self):
-    if self.role not in ("matrix", "table", "vector", "int"):
+    if self.role not in ("matrix", "table", "vector", "matrix_f32", "int"):
       raise ValueError(f"unknown parameter role {self.role!r}")
 
 

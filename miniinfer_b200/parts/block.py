@@ -43,3 +43,28 @@ class PreNormBlock(Block):
       return None
     x = self.ffn_norm.add_norm(resid, a, ctx)
     return self.ffn.forward(x, ctx)
+
+
+class ParallelBlock(Block):
+  """One norm a layer; mixer and feed-forward both read its output: with ``h = norm(x)``, ``x <- x + (mixer(h) + ff(h))``.
+  The two outputs are left pending as a pair and added, in float32, by the norm that comes next.  ``ffn`` may be None
+  (a layer without a feed-forward)."""
+
+  def __init__(self, name: str, norm: Norm, mixer: Mixer, ffn: Optional[FeedForward]):
+    super().__init__(name)
+    self.norm = norm
+    self.mixer = mixer
+    self.ffn = ffn
+
+  def sub_parts(self) -> List[Part]:
+    return [self.norm, self.mixer] + ([self.ffn] if self.ffn is not None else [])
+
+  def mixer_part(self) -> Optional[Mixer]:
+    return self.mixer
+
+  def forward(self, resid: torch.Tensor, pending, ctx, cache):
+    x = self.norm.add_norm(resid, pending, ctx)
+    a = self.mixer.forward(x, ctx, cache)
+    if self.ffn is None:
+      return a
+    return (a, self.ffn.forward(x, ctx))

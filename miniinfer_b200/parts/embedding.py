@@ -18,33 +18,43 @@ from .base import Embedding, Head, ParamSpec, whole
 
 
 class TokenEmbedding(Embedding):
-  def __init__(self, name: str, vocab_size: int, hidden_size: int):
+  """``scale``: a constant the looked-up row is multiplied with (1: none).  ``tensor``: the table's name in the weights
+  file (default ``<name>.weight``)."""
+
+  def __init__(self, name: str, vocab_size: int, hidden_size: int, scale: float = 1.0, tensor: Optional[str] = None):
     super().__init__(name)
     self.vocab_size = vocab_size
     self.hidden_size = hidden_size
+    self.scale = float(scale)
+    self.tensor = tensor or f"{name}.weight"
 
   def param_specs(self) -> Dict[str, ParamSpec]:
     shape = (self.vocab_size, self.hidden_size)
-    return {"weight": ParamSpec(shape, "table", [whole(f"{self.name}.weight", shape)])}
+    return {"weight": ParamSpec(shape, "table", [whole(self.tensor, shape)])}
 
   def forward(self, ids: torch.Tensor, ctx) -> torch.Tensor:
     out = ctx.ws.buffer("resid", (ids.shape[0], self.hidden_size), torch.float32)
-    ops.embedding(out, self.weight, ids)
+    if self.scale == 1.0:
+      ops.embedding(out, self.weight, ids)
+    else:
+      ops.embedding(out, self.weight, ids, self.scale)
     return out
 
 
 class LMHead(Head):
-  def __init__(self, name: str, vocab_size: int, hidden_size: int, tied_to: Optional[TokenEmbedding] = None):
+  def __init__(self, name: str, vocab_size: int, hidden_size: int, tied_to: Optional[TokenEmbedding] = None,
+               tensor: Optional[str] = None):
     super().__init__(name)
     self.vocab_size = vocab_size
     self.hidden_size = hidden_size
     self.tied_to = tied_to
+    self.tensor = tensor or f"{name}.weight"
 
   def param_specs(self) -> Dict[str, ParamSpec]:
     if self.tied_to is not None:
       return {}
     shape = (self.vocab_size, self.hidden_size)
-    return {"weight": ParamSpec(shape, "matrix", [whole(f"{self.name}.weight", shape)])}
+    return {"weight": ParamSpec(shape, "matrix", [whole(self.tensor, shape)])}
 
   def validate(self, dtype: torch.dtype) -> None:
     if dtype == torch.bfloat16 and self.hidden_size % 8:

@@ -4,7 +4,7 @@
 
 from __future__ import annotations
 
-from typing import Dict
+from typing import Dict, Optional, Tuple
 
 import torch
 
@@ -13,13 +13,21 @@ from .base import FeedForward, ParamSpec, Piece, whole
 
 
 class SwiGLUFeedForward(FeedForward):
-  def __init__(self, name: str, hidden_size: int, intermediate_size: int):
+  """``tensors``: the file names of the gate, up and down matrices after ``<name>.`` (default: ``gate_proj.weight``,
+  ``up_proj.weight``, ``down_proj.weight``, with ``gate_up_proj.weight`` accepted for the fused pair)."""
+
+  def __init__(self, name: str, hidden_size: int, intermediate_size: int, tensors: Optional[Tuple[str, str, str]] = None):
     super().__init__(name)
     self.hidden_size = hidden_size
     self.intermediate_size = intermediate_size
+    self.tensors = tensors
 
   def param_specs(self) -> Dict[str, ParamSpec]:
     H, I = self.hidden_size, self.intermediate_size
+    if self.tensors is not None:
+      g, u, d = (f"{self.name}.{t}" for t in self.tensors)
+      return {"gate_up": ParamSpec((2 * I, H), "matrix", [[Piece(g, 0, (I, H)), Piece(u, I, (I, H))]]),
+              "down": ParamSpec((H, I), "matrix", [whole(d, (H, I))])}
     return {
       "gate_up": ParamSpec((2 * I, H), "matrix", [
         [Piece(f"{self.name}.gate_proj.weight", 0, (I, H)), Piece(f"{self.name}.up_proj.weight", I, (I, H))],
@@ -50,4 +58,50 @@ class SwiGLUFeedForward(FeedForward):
     ops.linear_swiglu(act, x, self.gate_up, ctx.ws)
     out = ctx.ws.buffer("ffn_out", (T, self.hidden_size), ctx.dtype)
     ops.linear(out, act, self.down)
+    return out
+
+
+class RoutedExpertsFeedForward(FeedForward):
+  """A mixture of ``num_experts`` small SwiGLU feed-forward layers of which each token uses ``top``.
+
+  Router logits ``z = W_router h`` and scores ``s = sigmoid(z)`` in float32 (the router matrix is kept in float32; ``h``
+  is the normalised row in the compute dtype).  The experts of the ``top`` largest ``s + correction`` are chosen;
+  their weights are their ``s`` (without the correction) divided by the sum of those ``s`` (+ 1e-20); the output is
+  the weighted sum of the chosen experts' outputs.  The experts' matrices are stacked: ``gate_up [E, 2 ff, H]`` (an
+  expert's gate rows, then its up rows), ``down [E, H, ff]``.  File tensors: ``<name>.router``, ``<name>.correction``,
+  ``<name>.e<i>.gate`` / ``.up`` / ``.down``."""
+
+  def __init__(self, name: str, hidden_size: int, expert_size: int, num_experts: int, top: int):
+    super().__init__(name)
+    if not (1 <= top <= num_experts):
+      raise ValueError(f"{name}: top={top} must lie in 1..experts={num_experts}")
+    self.hidden_size = hidden_size
+    self.expert_size = expert_size
+    self.num_experts = num_experts
+    self.top = top
+
+  def param_specs(self) -> Dict[str, ParamSpec]:
+    H, F, E, n = self.hidden_size, self.expert_size, self.num_experts, self.name
+    gate_up = [p for e in range(E) for p in (Piece(f"{n}.e{e}.gate", 2 * F * e, (F, H)), Piece(f"{n}.e{e}.up", 2 * F * e + F, (F, H)))]
+    down = [Piece(f"{n}.e{e}.down", H * e, (H, F)) for e in range(E)]
+    return {
+      "router": ParamSpec((E, H), "matrix_f32", [whole(f"{n}.router", (E, H))]),
+      "correction": ParamSpec((E,), "vector", [whole(f"{n}.correction", (E,))]),
+      "gate_up": ParamSpec((2 * F * E, H), "matrix", [gate_up]),
+      "down": ParamSpec((H * E, F), "matrix", [down]),
+    }
+
+  def validate(self, dtype: torch.dtype) -> None:
+    if self.num_experts > 256 or self.top > 32:
+      raise ValueError(f"{self.name}: the routing kernel takes up to 256 experts and top up to 32")
+    if dtype == torch.bfloat16:
+      for what, k in (("hidden_size", self.hidden_size), ("expert_size", self.expert_size)):
+        if k % 8:
+          raise ValueError(f"{self.name}: {what}={k} must be a multiple of 8 in bfloat16 (rows are read 16 bytes at a time)")
+
+  def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
+    H, F, E = self.hidden_size, self.expert_size, self.num_experts
+    out = ctx.ws.buffer("ffn_out", (x.shape[0], H), ctx.dtype)
+    ops.routed_experts(out, x, self.router, self.correction, self.gate_up.view(E, 2 * F, H), self.down.view(E, H, F),
+                       self.top, ctx.ws)
     return out

@@ -1,0 +1,123 @@
+"""Windowed grouped-query attention without rotation, with unit-norm queries and keys, a sink in the softmax, values
+mixed across layers and an output gate, as a mixer part over the paged cache.
+
+For the normalised rows ``h`` of a step, with ``H`` query heads, ``G`` key/value heads (query head ``i`` reads
+key/value head ``i // (H / G)``), query/key size ``dim`` and value size ``vdim``:
+
+  * one fused product gives ``q``, ``k``, ``v`` and the gate's logits ``g`` (no biases);
+  * every head of ``q`` and ``k`` is divided by its root mean square, ``x / sqrt(mean(x^2) + eps)`` (float32; no weight);
+    positions do not enter the scores;
+  * ``value_mix="mixed"``: ``v <- (1 - lambda) v + lambda v_src`` with ``lambda`` a learned scalar and ``v_src`` the
+    values that the layer with ``value_mix="source"`` made for the same token in this step (handed on through
+    ``ctx.shared[value_mix_key]``); what is cached is the mixed ``v`` and the normalised ``k``;
+  * token ``i`` sees token ``j`` of its request if ``0 <= i - j < window`` (``window`` None: every earlier token);
+  * ``softmax`` over ``scale * q . k`` whose denominator also holds ``exp(sink)`` of the query head (``sinks``), a term
+    with no key and no value;
+  * the heads' outputs, side by side, are multiplied element by element with ``sigmoid(g)`` (``gated``), then projected.
+
+Every option can be switched off, so other designs may take the parts they need.  The cache keeps keys and values in
+rows of one size, ``max(dim, vdim)`` rounded up to a multiple of 16 and zero-filled: a zero tail adds nothing to a score,
+and the kernels write only the first ``vdim`` values of an output head.
+"""
+
+from __future__ import annotations
+
+from typing import Dict, List, Optional
+
+import torch
+
+from ..cache.specs import CacheSpec, PagedKVSpec
+from ..kernels import ops
+from .base import ParamSpec, Piece, StepWork, whole
+from .mixer import AttentionMixer
+
+
+class GatedAttentionMixer(AttentionMixer):
+  def __init__(self, name: str, hidden_size: int, num_heads: int, num_kv_heads: int, dim: int, vdim: int, scale: float,
+               norm_eps: Optional[float], window: Optional[int] = None, sinks: bool = True, gated: bool = True,
+               value_mix: Optional[str] = None, value_mix_key: str = "value_mix_source",
+               tensors: Optional[Dict[str, str]] = None):
+    super().__init__(name, hidden_size, num_heads, num_kv_heads, dim, scale, norm_eps, None, window)
+    if value_mix not in (None, "source", "mixed"):
+      raise ValueError(f"{name}: value_mix must be None, 'source' or 'mixed', got {value_mix!r}")
+    if dim <= 0 or vdim <= 0:
+      raise ValueError(f"{name}: dim and vdim must be positive")
+    self.dim = dim
+    self.vdim = vdim
+    self.cache_head_dim = -(-max(dim, vdim) // 16) * 16
+    self.sinks = sinks
+    self.gated = gated
+    self.value_mix = value_mix
+    self.value_mix_key = value_mix_key
+    t = {"q": "q", "k": "k", "v": "v", "g": "g", "o": "o", "sink": "sink", "mix": "vmix"}
+    t.update(tensors or {})
+    self.tensors = t
+    H, G = num_heads, num_kv_heads
+    self.q_off = 0
+    self.k_off = H * dim
+    self.v_off = self.k_off + G * dim
+    self.g_off = self.v_off + G * vdim
+    self.proj_width = self.g_off + (H * vdim if gated else 0)
+
+  def cache_spec(self) -> Optional[CacheSpec]:
+    return PagedKVSpec(self.num_kv_heads, self.cache_head_dim, self.window)
+
+  def param_specs(self) -> Dict[str, ParamSpec]:
+    Hd, H, G, D, Dv, n, t = self.hidden_size, self.num_heads, self.num_kv_heads, self.dim, self.vdim, self.name, self.tensors
+    pieces = [Piece(f"{n}.{t['q']}", self.q_off, (H * D, Hd)), Piece(f"{n}.{t['k']}", self.k_off, (G * D, Hd)),
+              Piece(f"{n}.{t['v']}", self.v_off, (G * Dv, Hd))]
+    if self.gated:
+      pieces.append(Piece(f"{n}.{t['g']}", self.g_off, (H * Dv, Hd)))
+    specs = {"qkvg": ParamSpec((self.proj_width, Hd), "matrix", [pieces]),
+             "o": ParamSpec((Hd, H * Dv), "matrix", [whole(f"{n}.{t['o']}", (Hd, H * Dv))])}
+    if self.sinks:
+      specs["sink"] = ParamSpec((H,), "vector", [whole(f"{n}.{t['sink']}", (H,))])
+    if self.value_mix is not None:
+      # the layer whose values are the source carries the scalar too (unused), as its file does
+      specs["mix"] = ParamSpec((), "vector", [whole(f"{n}.{t['mix']}", ())], init="half_noise")
+    return specs
+
+  def validate(self, dtype: torch.dtype) -> None:
+    if self.cache_head_dim > 256:
+      raise ValueError(f"{self.name}: head sizes up to 256 are supported, got dim={self.dim}, vdim={self.vdim}")
+    if dtype == torch.bfloat16:
+      for what, k in (("width", self.hidden_size), ("heads * vdim", self.num_heads * self.vdim),
+                      ("the fused projection's rows", self.proj_width)):
+        if k % 8:
+          raise ValueError(f"{self.name}: {what}={k} must be a multiple of 8 in bfloat16 (rows are read 16 bytes at a time)")
+
+  def step_work(self) -> List[StepWork]:
+    return super().step_work()
+
+  def takes_residual(self, norm, ctx) -> bool:
+    return False
+
+  def forward(self, x: torch.Tensor, ctx, cache) -> torch.Tensor:
+    T = x.shape[0]
+    H, G, D, Dv, hdp = self.num_heads, self.num_kv_heads, self.dim, self.vdim, self.cache_head_dim
+    if cache.kind != "paged":
+      raise RuntimeError(f"{self.name}: attention needs a paged cache, got {cache.kind!r}")
+    proj = ctx.ws.buffer("qkvg", (T, self.proj_width), ctx.dtype)
+    ops.linear(proj, x, self.qkvg)
+    q_heads = ctx.ws.buffer("q_heads", (T, H * hdp), ctx.dtype)
+    v_other, v_mode, mix = None, 0, None
+    if self.value_mix == "source":
+      v_other = ctx.ws.buffer(f"values:{self.value_mix_key}", (T, G * Dv), ctx.dtype)
+      ctx.shared[self.value_mix_key] = v_other
+      v_mode = 1
+    elif self.value_mix == "mixed":
+      v_other = ctx.shared.get(self.value_mix_key)
+      if v_other is None or v_other.shape != (T, G * Dv):
+        raise RuntimeError(f"{self.name}: no layer before this one has left its values under {self.value_mix_key!r}")
+      v_mode, mix = 2, self.mix
+    ops.qkv_norm_mix_store(proj, self.q_off, self.k_off, self.v_off, q_heads, H, G, D, Dv,
+                           self.qk_norm_eps if self.qk_norm_eps is not None else 1.0, self.qk_norm_eps is not None,
+                           None, None, mix, v_other, v_mode,
+                           ctx.slot_mapping[cache.group] if cache.writes else None, cache.tensor if cache.writes else None)
+    attn = ctx.ws.buffer("attn_out", (T, H * Dv), ctx.dtype)
+    ops.attention(attn, q_heads, cache.tensor, ctx.block_tables[cache.group], self._batch(ctx), H, G, hdp, self.scale,
+                  self.window, sink=self.sink if self.sinks else None, gate=proj if self.gated else None,
+                  gate_offset=self.g_off, out_hd=Dv)
+    out = ctx.ws.buffer("mixer_out", (T, self.hidden_size), ctx.dtype)
+    ops.linear(out, attn, self.o)
+    return out

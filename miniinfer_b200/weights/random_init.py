@@ -28,6 +28,8 @@ def _draw(shape, init: str, std: float, gen: torch.Generator, device="cpu") -> t
   t = torch.randn(tuple(shape), generator=gen, dtype=torch.float32, device=device)
   if init == "ones_noise":
     return 1.0 + NORM_NOISE * t
+  if init == "half_noise":
+    return 0.5 + NORM_NOISE * t
   return std * t
 
 
@@ -77,7 +79,7 @@ def init_random_on_device(spec: ModelSpec, compute_dtype: torch.dtype, device, s
         continue
       p = torch.empty(ps.shape, dtype=dt, device=device)
       rows = max(1, (1 << 26) // max(1, int(torch.tensor(ps.shape[1:]).prod()) if len(ps.shape) > 1 else 1))
-      if len(ps.shape) == 1:
+      if len(ps.shape) <= 1:
         p.copy_(_draw(ps.shape, ps.init, spec.init_std, gen, device))
       else:
         for r0 in range(0, ps.shape[0], rows):

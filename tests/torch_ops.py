@@ -17,8 +17,25 @@ from typing import Optional
 import torch
 
 
-def embedding(out, table, ids):
-  out.copy_(table[ids.long()].float())
+def embedding(out, table, ids, scale=1.0):
+  out.copy_(table[ids.long()].float() * scale)
+
+
+def add_layernorm(out, resid, delta, delta2, weight, bias, eps, rows=None, write_back=True):
+  idx = rows.long() if rows is not None else None
+  x = resid if idx is None else resid[idx]
+  ds = [d for d in (delta, delta2) if d is not None]
+  if ds:
+    add = ds[0].float() if len(ds) == 1 else ds[0].float() + ds[1].float()
+    x = x + (add if idx is None else add[idx])
+    if write_back:
+      if idx is None:
+        resid.copy_(x)
+      else:
+        resid[idx] = x
+  mu = x.mean(-1, keepdim=True)
+  var = ((x - mu) ** 2).mean(-1, keepdim=True)
+  out.copy_(((x - mu) / torch.sqrt(var + eps) * weight + bias).to(out.dtype))
 
 
 def add_rmsnorm(out, resid, delta, weight, eps, rows=None, write_back=True):
@@ -91,8 +108,65 @@ def qk_norm_rope_store(qkv, q_weight, k_weight, cos_sin, positions, slot_mapping
     kv_layer[page, 1, :, off, :] = r[ok, nh + nkv:]
 
 
+def qkv_norm_mix_store(proj, q_off, k_off, v_off, q_out, num_heads, num_kv_heads, dim, vdim, eps, normalise=True,
+                       q_weight=None, k_weight=None, mix=None, v_other=None, v_mode=0, slot_mapping=None, kv_layer=None):
+  T = proj.shape[0]
+  H, G = num_heads, num_kv_heads
+  hdp = q_out.shape[1] // H
+  x = proj.float()
+  q = x[:, q_off:q_off + H * dim].reshape(T, H, dim)
+  k = x[:, k_off:k_off + G * dim].reshape(T, G, dim)
+  v = x[:, v_off:v_off + G * vdim].reshape(T, G, vdim)
+  if normalise:
+    q = q / torch.sqrt(q.pow(2).mean(-1, keepdim=True) + eps)
+    k = k / torch.sqrt(k.pow(2).mean(-1, keepdim=True) + eps)
+  if q_weight is not None:
+    q = q * q_weight
+  if k_weight is not None:
+    k = k * k_weight
+  if v_mode == 1:
+    v_other.copy_(v.reshape(T, G * vdim).to(v_other.dtype))
+  elif v_mode == 2:
+    lam = mix.float()
+    v = (1 - lam) * v + lam * v_other.float().reshape(T, G, vdim)
+  qp = torch.zeros((T, H, hdp), dtype=torch.float32, device=proj.device)
+  qp[..., :dim] = q
+  q_out.copy_(qp.reshape(T, H * hdp).to(q_out.dtype))
+  if slot_mapping is not None and kv_layer is not None:
+    P = kv_layer.shape[3]
+    slot = slot_mapping.long()
+    page, off = slot // P, slot % P
+    kp = torch.zeros((T, G, hdp), dtype=torch.float32, device=proj.device)
+    vp = torch.zeros((T, G, hdp), dtype=torch.float32, device=proj.device)
+    kp[..., :dim] = k
+    vp[..., :vdim] = v
+    kv_layer[page, 0, :, off, :] = kp.to(kv_layer.dtype)
+    kv_layer[page, 1, :, off, :] = vp.to(kv_layer.dtype)
+
+
+def routed_experts(out, x, router, correction, gate_up, down, top, workspace):
+  T, H = x.shape
+  E, ff = router.shape[0], down.shape[2]
+  z = x.float() @ router.float().t()
+  s = torch.sigmoid(z)
+  idx = torch.topk(s + correction, top, dim=-1).indices
+  w = torch.gather(s, 1, idx)
+  w = w / (w.sum(-1, keepdim=True) + 1e-20)
+  res = torch.zeros((T, H), dtype=torch.float32, device=x.device)
+  for e in range(E):
+    g = x.float() @ gate_up[e, :ff].float().t()
+    u = x.float() @ gate_up[e, ff:].float().t()
+    act = (g * torch.sigmoid(g) * u).to(x.dtype).float()
+    y = act @ down[e].float().t()
+    res += (w * (idx == e)).sum(-1, keepdim=True) * y
+  out.copy_(res.to(out.dtype))
+
+
 def attention(out, qkv, kv_layer, block_table, batch, num_heads, num_kv_heads, head_dim, scale, window,
-              force_generic=False):
+              force_generic=False, sink=None, gate=None, gate_offset=0, out_hd=None):
+  if sink is not None or gate is not None or (out_hd is not None and out_hd != head_dim):
+    return _attention_with_options(out, qkv, kv_layer, block_table, batch, num_heads, num_kv_heads, head_dim, scale,
+                                   window, sink, gate, gate_offset, out_hd if out_hd is not None else head_dim)
   T = qkv.shape[0]
   nh, nkv, hd = num_heads, num_kv_heads, head_dim
   P = kv_layer.shape[3]
@@ -115,6 +189,31 @@ def attention(out, qkv, kv_layer, block_table, batch, num_heads, num_kv_heads, h
     pr = torch.softmax(s, dim=-1)
     res[t] = torch.einsum("hn,nhd->hd", pr, v)
   out.copy_(res.reshape(T, nh * hd).to(out.dtype))
+
+
+def _attention_with_options(out, qkv, kv_layer, block_table, batch, nh, nkv, hd, scale, window, sink, gate, gate_offset, ohd):
+  T = qkv.shape[0]
+  P = kv_layer.shape[3]
+  g = nh // nkv
+  q = qkv.float().view(T, -1, hd)[:, :nh]
+  pos, item, slots = batch.positions.tolist(), batch.token_item.tolist(), batch.seq_slot.tolist()
+  res = torch.zeros((T, nh, ohd), dtype=torch.float32, device=qkv.device)
+  for t in range(T):
+    p = pos[t]
+    lo = max(0, p - window + 1) if window else 0
+    js = torch.arange(lo, p + 1, device=qkv.device)
+    pages = block_table[slots[item[t]]].long()[js // P]
+    k = kv_layer[pages, 0, :, js % P, :].float().repeat_interleave(g, dim=1)
+    v = kv_layer[pages, 1, :, js % P, :].float().repeat_interleave(g, dim=1)
+    s = torch.einsum("hd,nhd->hn", q[t], k) * scale
+    if sink is not None:
+      s = torch.cat((s, sink.float()[:, None]), dim=1)
+    pr = torch.softmax(s, dim=-1)[:, :js.numel()]
+    res[t] = torch.einsum("hn,nhd->hd", pr, v)[:, :ohd]
+  res = res.reshape(T, nh * ohd)
+  if gate is not None:
+    res = res * torch.sigmoid(gate.float()[:, gate_offset:gate_offset + nh * ohd])
+  out.copy_(res.to(out.dtype))
 
 
 def linear_swiglu(out, x, w, workspace, force_skinny=False, force_tc=False):
@@ -176,6 +275,6 @@ def install(monkeypatch) -> None:
   """Puts the statements above in place of the CUDA kernels (CPU tests of the host-side logic)."""
   from miniinfer_b200.kernels import ops
 
-  for name in ("embedding", "add_rmsnorm", "linear", "linear_swiglu", "qk_norm_rope_store", "attention", "silu_mul", "sample",
-               "linear_normed", "linear_swiglu_normed", "linear_add"):
+  for name in ("embedding", "add_rmsnorm", "add_layernorm", "linear", "linear_swiglu", "qk_norm_rope_store", "qkv_norm_mix_store",
+               "attention", "routed_experts", "silu_mul", "sample", "linear_normed", "linear_swiglu_normed", "linear_add"):
     monkeypatch.setattr(ops, name, globals()[name])
