@@ -652,13 +652,180 @@ def reference_arm(args) -> int:
   return 0
 
 
+# ---------------------------------------------------------------------------------------------- --compare rikanex
+# Sizes for the comparison of the Rikanex design with the Qwen3 dense decoder at equal size: width, query / kv heads, head
+# size, the dense feed-forward's width, and the experts that stand for it (count, width, per token) so that a token
+# passes through as many feed-forward weights in both; layers; both models get the same sliding window and vocabulary.
+COMPARE_SIZES = {
+  "s": dict(width=1024, heads=16, kv_heads=8, head=128, ff=3072, experts=8, expert_ff=768, top=4, layers=8),
+  "m": dict(width=2048, heads=32, kv_heads=8, head=64, ff=6144, experts=16, expert_ff=1536, top=4, layers=6),
+  "l": dict(width=4096, heads=32, kv_heads=8, head=128, ff=12288, experts=32, expert_ff=1536, top=8, layers=4),
+}
+COMPARE_WINDOW = 1024
+COMPARE_VOCAB = 32768
+
+
+def compare_configs(size: dict) -> dict:
+  W, H, G, hd = size["width"], size["heads"], size["kv_heads"], size["head"]
+  qwen = dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", num_hidden_layers=size["layers"], hidden_size=W,
+              num_attention_heads=H, num_key_value_heads=G, head_dim=hd, intermediate_size=size["ff"], vocab_size=COMPARE_VOCAB,
+              rope_theta=1000000.0, rms_norm_eps=1e-6, max_position_embeddings=40960, tie_word_embeddings=False,
+              use_sliding_window=True, sliding_window=COMPARE_WINDOW, max_window_layers=0)
+  mixer = {"heads": H, "kv_heads": G, "dim": hd, "vdim": hd, "scale": hd ** -0.5, "mask": {"size": COMPARE_WINDOW}, "v_mix": True}
+  moe = {"kind": "moe", "expert": {"ff": size["expert_ff"]}, "router": {"experts": size["experts"], "top": size["top"]}}
+  layers = [{"type": "attention", "mixer": dict(mixer), "mlp": {"kind": "dense", "ff": size["ff"]} if i == 0 else moe}
+            for i in range(size["layers"])]
+  rikanex = {"architecture": "Rikanex", "vocab": COMPARE_VOCAB, "width": W, "embedding": {"scale": 8.0}, "norm": {"eps": 1e-6},
+             "layers": layers}
+  return {"qwen3": qwen, "rikanex": rikanex}
+
+
+def _compare_groups(times: dict) -> dict:
+  import re
+  g = {"attention": 0.0, "experts": 0.0, "dense_products": 0.0, "routing": 0.0, "other": 0.0}
+  for name, us in times.items():
+    if re.search(r"decode_tma_kernel|decode_cluster_kernel|decode_split_kernel|decode_merge|attention_prefill|attention_generic", name):
+      g["attention"] += us
+    elif "moe_gemm" in name:
+      g["experts"] += us
+    elif re.search(r"moe_route|moe_align|moe_combine", name):
+      g["routing"] += us
+    elif "gemm_skinny" in name or "gemm_tc_kernel" in name or "gemm_stream_tc" in name or \
+        ("anonymous namespace" not in name and re.search(r"nvjet|cutlass|cublas|gemm|gemv|xmma", name, re.I)):
+      g["dense_products"] += us
+    elif not name.startswith("Memcpy") and not name.startswith("Memset"):
+      g["other"] += us
+  return g
+
+
+def compare_one(name: str, cfg: dict, size: dict, batch: int, steps: int, warmup: int, pk: dict, kernels: bool) -> dict:
+  """Prefill and decode of one model of the comparison; with ``kernels`` the device time of its kinds of kernels and the
+  rates they reach against the measured peaks (run with dependent launch off, see main)."""
+  import torch
+  from miniinfer_b200.engine import StepItem
+  from miniinfer_b200.sampling import Sampler, SamplingParams
+  W, H, G, hd, L = size["width"], size["heads"], size["kv_heads"], size["head"], size["layers"]
+  win, T = COMPARE_WINDOW, PREFILL_TOKENS
+  with tempfile.TemporaryDirectory() as d:
+    with open(os.path.join(d, "config.json"), "w") as f:
+      json.dump(cfg, f)
+    engine = build_engine(d, batch)
+    out = {}
+    if not kernels:
+      dec = time_decode(engine, batch, steps, warmup)
+      pre = time_prefill(engine)
+      out = {"decode_tok_s": round(dec["tok_s"], 1), "decode_ms": round(dec["ms"], 4), "launches_per_decode_step": int(dec["launches_per_step"]),
+             "prefill_tok_s": round(T / (pre["ms"] * 1e-3), 1), "prefill_ms": round(pre["ms"], 3)}
+    else:
+      rids = fill_context(engine, batch, CONTEXT, seed=1000 + batch)
+      params = [SamplingParams(temperature=0.6, max_tokens=GENERATED, ignore_eos=True)] * batch
+      tokens_dev = torch.zeros(max(batch, 1), dtype=torch.int32, device="cuda:0")
+
+      def decode(i):
+        extras = Sampler.pack(params, list(range(batch)), [i] * batch)
+        engine.runner.step_and_sample([StepItem(r, [1], (0,)) for r in rids], extras, Sampler.sample, tokens_dev,
+                                      sampling_pad=Sampler.PAD_ROWS)
+
+      for i in range(4):
+        decode(i)
+      torch.cuda.synchronize()
+      dk = _compare_groups(_kernel_times(lambda i: decode(10 + i), 4))
+      for r in rids:
+        engine.cache.release_request(r)
+      g = torch.Generator().manual_seed(7)
+
+      def whole(i):
+        rid = f"rates{i}"
+        engine.cache.admit(rid)
+        engine.runner.step([StepItem(rid, torch.randint(0, COMPARE_VOCAB, (T,), generator=g).tolist(), (T - 1,))])
+        engine.cache.release_request(rid)
+
+      for i in range(2):
+        whole(i)
+      torch.cuda.synchronize()
+      pk_times = _compare_groups(_kernel_times(lambda i: whole(10 + i), 2))
+      # what each kind of kernel has to do
+      seen = sum(min(t + 1, win) for t in range(T))
+      attn_flops = L * 4.0 * H * hd * seen
+      attn_bytes = batch * min(CONTEXT, win) * L * 2 * G * hd * 2
+      moe_layers = L - 1 if name == "rikanex" else 0
+      E, F, top = size["experts"], size["expert_ff"], size["top"]
+      touched = E * (1.0 - (1.0 - top / E) ** batch)             # experts a decode step of `batch` tokens reads, on average
+      rates = {"prefill_attention": {"us": round(pk_times["attention"], 1), "TFLOP/s": round(attn_flops / pk_times["attention"] / 1e6, 1),
+                                     "frac": round(attn_flops / pk_times["attention"] / 1e6 / pk["bf16_tflops"], 4)},
+               "decode_attention": {"us": round(dk["attention"], 1), "GB/s": round(attn_bytes / dk["attention"] / 1e3, 1),
+                                    "frac": round(attn_bytes / dk["attention"] / 1e3 / pk["hbm_gbs"], 4)}}
+      if moe_layers:
+        moe_flops = moe_layers * T * top * 3 * 2.0 * F * W
+        moe_bytes = moe_layers * touched * 3 * F * W * 2
+        rates["prefill_experts"] = {"us": round(pk_times["experts"], 1), "TFLOP/s": round(moe_flops / pk_times["experts"] / 1e6, 1),
+                                    "frac": round(moe_flops / pk_times["experts"] / 1e6 / pk["bf16_tflops"], 4)}
+        rates["decode_experts"] = {"us": round(dk["experts"], 1), "GB/s": round(moe_bytes / dk["experts"] / 1e3, 1),
+                                   "frac": round(moe_bytes / dk["experts"] / 1e3 / pk["hbm_gbs"], 4)}
+        rates["routing_us"] = {"prefill": round(pk_times["routing"], 1), "decode": round(dk["routing"], 1)}
+      dense_ff = (L - moe_layers) * 3 * size["ff"] * W
+      proj = L * ((H + 2 * G) * hd * W + W * H * hd + (H * hd * W if name == "rikanex" else 0))
+      dense_w = dense_ff + proj + COMPARE_VOCAB * W
+      rates["prefill_dense_products"] = {"us": round(pk_times["dense_products"], 1),
+                                         "TFLOP/s": round(2.0 * T * (dense_ff + proj) / pk_times["dense_products"] / 1e6, 1),
+                                         "frac": round(2.0 * T * (dense_ff + proj) / pk_times["dense_products"] / 1e6 / pk["bf16_tflops"], 4)}
+      rates["decode_dense_products"] = {"us": round(dk["dense_products"], 1), "GB/s": round(2.0 * dense_w / dk["dense_products"] / 1e3, 1),
+                                        "frac": round(2.0 * dense_w / dk["dense_products"] / 1e3 / pk["hbm_gbs"], 4)}
+      rates["other_us"] = {"prefill": round(pk_times["other"], 1), "decode": round(dk["other"], 1)}
+      out = rates
+    engine.stop()
+    del engine
+    gc.collect()
+    torch.cuda.empty_cache()
+  return out
+
+
+def compare_designs(args) -> int:
+  """``--compare rikanex``: the Rikanex design beside the Qwen3 dense decoder at equal sizes (random weights): prefill of
+  one 2048-token prompt and decode steps at ``--batch`` requests with ``--context``-token contexts, and, from a process of
+  its own with dependent launch off, what the kinds of kernels of both reach against the measured peaks."""
+  pk = peaks()
+  warmup = max(args.warmup, 3)
+  global GENERATED, MAX_MODEL_LEN
+  GENERATED = max(GENERATED, warmup + args.steps + args.batch * -(-CONTEXT // PREFILL_TOKENS) + 64)
+  MAX_MODEL_LEN = max(MAX_MODEL_LEN, -(-(CONTEXT + GENERATED + 128) // 1024) * 1024)
+  sizes = [x for x in args.sizes.split(",") if x]
+  result = {"compare": "rikanex beside qwen3 at equal sizes", "batch": args.batch, "context": CONTEXT, "window": COMPARE_WINDOW,
+            "vocab": COMPARE_VOCAB, "prefill_tokens": PREFILL_TOKENS, "steps": args.steps, "warmup": warmup, "dtype": "bf16",
+            "data": "synthetic: random weights, uniform random token ids", "peaks": pk["source"], "sizes": {}}
+  kernels_child = args.impl == "compare-child"
+  for tag in sizes:
+    size = COMPARE_SIZES[tag]
+    row = {"size": size}
+    for name, cfg in compare_configs(size).items():
+      row[name] = compare_one(name, cfg, size, args.batch, args.steps, warmup, pk, kernels_child)
+    result["sizes"][tag] = row
+  if not kernels_child and not args.skip_kernels:
+    cmd = [sys.executable, os.path.abspath(__file__), "--impl", "compare-child", "--compare", "rikanex", "--sizes", args.sizes,
+           "--batch", str(args.batch), "--context", str(CONTEXT), "--steps", str(args.steps), "--warmup", str(warmup)]
+    proc = subprocess.run(cmd, capture_output=True, text=True, env=dict(os.environ, MINIINFER_B200_PDL="0"))
+    found = [l for l in proc.stdout.splitlines() if l.startswith('{"compare"')]
+    if found:
+      child = json.loads(found[-1])
+      for tag in sizes:
+        for name in ("qwen3", "rikanex"):
+          result["sizes"][tag][name]["kernels"] = child["sizes"][tag][name]
+    else:
+      result["kernels_unavailable"] = (proc.stderr or "no output").strip().splitlines()[-1][:300]
+  print(json.dumps(result))
+  return 0
+
+
 def main() -> int:
   global CONTEXT
   ap = argparse.ArgumentParser()
   ap.add_argument("--gpus", type=int, default=1)
   ap.add_argument("--steps", type=int, default=128)
   ap.add_argument("--warmup", type=int, default=8)
-  ap.add_argument("--impl", default="ours", choices=["ours", "reference", "reference-child", "kernels-child"])
+  ap.add_argument("--impl", default="ours", choices=["ours", "reference", "reference-child", "kernels-child", "compare-child"])
+  ap.add_argument("--compare", default=None, choices=["rikanex"],
+                  help="time the Rikanex design beside the Qwen3 dense decoder at equal sizes (--sizes), print one JSON line and exit")
+  ap.add_argument("--sizes", default="s,m,l", help="with --compare: which of the sizes s, m, l (commas between them)")
   ap.add_argument("--batch", type=int, default=8)
   ap.add_argument("--shape", default="0.6b", choices=sorted(SHAPES), help="layer sizes: the default, or another Qwen3 model's")
   ap.add_argument("--layers", type=int, default=None, help="fewer layers than the model has (named in config)")
@@ -675,6 +842,10 @@ def main() -> int:
   if args.kernel_case:
     print(kernel_case(args.kernel_case))
     return 0
+  if args.compare:
+    if args.context is not None:
+      CONTEXT = args.context
+    return compare_designs(args)
   if args.impl == "reference":
     return reference_arm(args)
   if args.impl == "reference-child":

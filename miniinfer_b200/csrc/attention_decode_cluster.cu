@@ -86,7 +86,25 @@ struct ClusterArgs {
   const int* slot_mapping;         // per row of the step: page * page_size + offset of the token's cache entry (null: no store)
   __nv_bfloat16* kv_layer;         // the layer's cache, [page][2][kv head][token][HD]
   float eps;
+  const float* sink;               // [nh] or null: a logit per query head whose exponential joins the denominator once
+  const __nv_bfloat16* gate;       // [T, gate_stride] or null: the output is multiplied with sigmoid(gate[row, head * HD + d])
+  int gate_stride;
 };
+
+// The last step of a head's output value: the sums A (weighted values) and L (weights) relative to the maximum M, the
+// sink as one more weight without a value, the gate.
+__device__ __forceinline__ __nv_bfloat16 finish_value(const ClusterArgs& a, float A, float L, float M, int row, int head, int d) {
+  if (a.sink) {
+    const float s2 = a.sink[head] * 1.4426950408889634f;      // base 2, like the scores
+    const float Mf = fmaxf(M, s2);
+    const float f = M == -INFINITY ? 0.f : exp2f(M - Mf);
+    L = L * f + exp2f(s2 - Mf);
+    A = A * f;
+  }
+  float y = A / L;
+  if (a.gate) y = __fdividef(y, 1.f + __expf(-__bfloat162float(a.gate[(size_t)row * a.gate_stride + (size_t)head * HD + d])));
+  return __float2bfloat16_rn(y);
+}
 
 __global__ void __launch_bounds__(CTHREADS, 1)
 decode_cluster_kernel(const __grid_constant__ CUtensorMap kv_map, ClusterArgs a) {
@@ -333,7 +351,7 @@ decode_cluster_kernel(const __grid_constant__ CUtensorMap kv_map, ClusterArgs a)
       }
     }
     if (C == 1) {
-      a.out[(size_t)row * a.nh * HD + (size_t)(kvh * G + h) * HD + d] = __float2bfloat16_rn(A / L);
+      a.out[(size_t)row * a.nh * HD + (size_t)(kvh * G + h) * HD + d] = finish_value(a, A, L, M, row, kvh * G + h, d);
     } else {
       const int owner = idx / slice;
       cluster.map_shared_rank(recv, owner)[(size_t)r * rs + (idx - owner * slice)] = A;
@@ -365,7 +383,7 @@ decode_cluster_kernel(const __grid_constant__ CUtensorMap kv_map, ClusterArgs a)
       L = fmaf(src[slice + 2 * h + 1], f, L);
       A = fmaf(src[t], f, A);
     }
-    a.out[(size_t)row * a.nh * HD + (size_t)(kvh * G + h) * HD + d] = __float2bfloat16_rn(A / L);
+    a.out[(size_t)row * a.nh * HD + (size_t)(kvh * G + h) * HD + d] = finish_value(a, A, L, M, row, kvh * G + h, d);
   }
 }
 
@@ -425,7 +443,8 @@ int launch_cluster(void* out, const void* q_base, int q_stride, const void* kv_m
                    const int* block_table, int bt_stride, const int* decode_items, const int* q_start,
                    const int* ctx_len, const int* seq_slot, int* status, int n_dec, int nh, int nkv,
                    int page_size, float scale, int window, int cluster, int max_ctx_len, cudaStream_t stream,
-                   int rope, const float* q_w, const float* k_w, const float* cos_sin, const int* slot_mapping, void* kv_layer, float eps) {
+                   int rope, const float* q_w, const float* k_w, const float* cos_sin, const int* slot_mapping, void* kv_layer, float eps,
+                   const float* sink = nullptr, const void* gate = nullptr, int gate_stride = 0) {
   MI_REQUIRE(n_dec >= 0 && nh > 0 && nkv > 0 && nh % nkv == 0, "attention_decode_cluster: bad head counts nh=%d nkv=%d", nh, nkv);
   MI_REQUIRE(nh / nkv <= GP, "attention_decode_cluster: at most %d query heads per kv head (got %d)", GP, nh / nkv);
   MI_REQUIRE(cluster >= 1 && cluster <= 16, "attention_decode_cluster: cluster=%d is not in 1..16", cluster);
@@ -435,6 +454,7 @@ int launch_cluster(void* out, const void* q_base, int q_stride, const void* kv_m
   MI_REQUIRE(((uintptr_t)q_base % 16) == 0, "attention_decode_cluster: q must be 16-byte aligned");
   if (n_dec == 0) return 0;
   ClusterArgs a;
+  a.sink = sink; a.gate = (const __nv_bfloat16*)gate; a.gate_stride = gate_stride;
   a.out = (__nv_bfloat16*)out;
   a.q_base = (const __nv_bfloat16*)q_base;
   a.q_stride = q_stride;
@@ -503,9 +523,11 @@ int launch_cluster(void* out, const void* q_base, int q_stride, const void* kv_m
 MI_API int mi_attention_decode_cluster(void* out, const void* q_base, int q_stride, const void* kv_map,
                                        const int* block_table, int bt_stride, const int* decode_items, const int* q_start,
                                        const int* ctx_len, const int* seq_slot, int* status, int n_dec, int nh, int nkv,
-                                       int page_size, float scale, int window, int cluster, int max_ctx_len, cudaStream_t stream) {
+                                       int page_size, float scale, int window, int cluster, int max_ctx_len, cudaStream_t stream,
+                                       const float* sink, const void* gate, int gate_stride) {
   return launch_cluster(out, q_base, q_stride, kv_map, block_table, bt_stride, decode_items, q_start, ctx_len, seq_slot, status, n_dec,
-                        nh, nkv, page_size, scale, window, cluster, max_ctx_len, stream, 0, nullptr, nullptr, nullptr, nullptr, nullptr, 0.f);
+                        nh, nkv, page_size, scale, window, cluster, max_ctx_len, stream, 0, nullptr, nullptr, nullptr, nullptr, nullptr, 0.f,
+                        sink, gate, gate_stride);
 }
 
 // The same for a step of decode tokens only, with the step before attention inside (head size 128, the whole head
@@ -526,7 +548,7 @@ MI_API int mi_attention_decode_cluster_rope(void* out, const void* qkv, int q_st
 MI_API int mi_attention_decode_cluster_supported() { return 0; }
 MI_API int mi_attention_decode_cluster_fit(int, int) { return 0; }
 MI_API int mi_attention_decode_cluster(void*, const void*, int, const void*, const int*, int, const int*, const int*, const int*,
-                                       const int*, int*, int, int, int, int, float, int, int, int, cudaStream_t) {
+                                       const int*, int*, int, int, int, int, float, int, int, int, cudaStream_t, const float*, const void*, int) {
   return mi_fail("attention_decode_cluster: head size %d has no such kernel", MI_HEAD_DIM);
 }
 MI_API int mi_attention_decode_cluster_rope(void*, const void*, int, const void*, const int*, int, const int*, const int*, const int*,

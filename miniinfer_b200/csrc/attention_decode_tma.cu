@@ -92,7 +92,15 @@ struct Args {
   int* status;
   int n_dec, nh, nkv, page_size, window, chunk, max_splits, stages, gp;   // gp = min(G, 16)
   float scale;
+  const float* sink;             // [nh] or null: a logit per query head whose exponential joins the denominator once
+  const __nv_bfloat16* gate;     // [T, gate_stride] or null: the output is multiplied with sigmoid(gate[row, head * HD + d])
+  int gate_stride;
 };
+
+__device__ __forceinline__ float gated(const Args& a, float y, int row, int head, int d) {
+  if (a.gate) y = __fdividef(y, 1.f + __expf(-__bfloat162float(a.gate[(size_t)row * a.gate_stride + (size_t)head * HD + d])));
+  return y;
+}
 
 __device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;" ::"n"(CONSUMERS * 32) : "memory"); }
 // Barrier of the consumer warps that also tells every one of them whether any passed a true flag.
@@ -323,9 +331,12 @@ decode_tma_kernel(const __grid_constant__ CUtensorMap kv_map, Args a) {
             float m = -INFINITY;
             for (int sp = lane; sp < ns; sp += 32) m = fmaxf(m, merge_s[2 * (gh * ns + sp)]);
             m = mi::warp_max(m);
+            const float sink2 = a.sink ? a.sink[d.kvh * G + gh] * 1.4426950408889634f : -INFINITY;   // base 2, like the scores
+            m = fmaxf(m, sink2);
             float l = 0.f;
             for (int sp = lane; sp < ns; sp += 32) l = fmaf(merge_s[2 * (gh * ns + sp) + 1], exp2f(merge_s[2 * (gh * ns + sp)] - m), l);
             l = mi::warp_sum(l);
+            if (a.sink) l += exp2f(sink2 - m);
             const float inv = 1.f / l;
             __syncwarp();
             for (int sp = lane; sp < ns; sp += 32) merge_s[2 * (gh * ns + sp)] = exp2f(merge_s[2 * (gh * ns + sp)] - m) * inv;   // the chunk's weight
@@ -352,7 +363,7 @@ decode_tma_kernel(const __grid_constant__ CUtensorMap kv_map, Args a) {
 #pragma unroll
               for (int i = 0; i < DS; ++i) {
                 const int dd = i * 32 + lane;
-                if (dd < HD) a.out[(size_t)d.row * a.nh * HD + (size_t)head * HD + dd] = __float2bfloat16_rn(acc[i]);
+                if (dd < HD) a.out[(size_t)d.row * a.nh * HD + (size_t)head * HD + dd] = __float2bfloat16_rn(gated(a, acc[i], d.row, head, dd));
               }
             }
 #pragma unroll
@@ -461,7 +472,15 @@ decode_tma_kernel(const __grid_constant__ CUtensorMap kv_map, Args a) {
         }
         const int head = d.kvh * G + g0 + r;
         if (d.n_splits == 1) {            // the only chunk: this is the output
-          a.out[(size_t)d.row * a.nh * HD + (size_t)head * HD + dd] = __float2bfloat16_rn(v / l);
+          float vf = v, lf = l;
+          if (a.sink) {
+            const float sink2 = a.sink[head] * 1.4426950408889634f;
+            const float mf = fmaxf(m, sink2);
+            const float f = m == -INFINITY ? 0.f : exp2f(m - mf);
+            vf = v * f;
+            lf = l * f + exp2f(sink2 - mf);
+          }
+          a.out[(size_t)d.row * a.nh * HD + (size_t)head * HD + dd] = __float2bfloat16_rn(gated(a, vf / lf, d.row, head, dd));
         } else {
           a.part_o[(((size_t)d.e * a.nh + head) * a.max_splits + d.split) * HD + dd] = v;
           if (dd == 0) {
@@ -525,7 +544,7 @@ MI_API int mi_attention_decode_tma(void* out, const void* q_base, int q_stride, 
                                    const int* block_table, int bt_stride, const int* decode_items, const int* q_start,
                                    const int* ctx_len, const int* seq_slot, float* scratch, int* counters, int* status,
                                    int n_dec, int nh, int nkv, int page_size, float scale, int window, int chunk,
-                                   int max_splits, int num_sms, cudaStream_t stream) {
+                                   int max_splits, int num_sms, cudaStream_t stream, const float* sink, const void* gate, int gate_stride) {
   MI_REQUIRE(n_dec >= 0 && nh > 0 && nkv > 0 && nh % nkv == 0, "attention_decode_tma: bad head counts nh=%d nkv=%d", nh, nkv);
   MI_REQUIRE(page_size % BK == 0, "attention_decode_tma: page_size=%d must be a multiple of %d", page_size, BK);
   MI_REQUIRE(chunk >= BK && chunk % BK == 0, "attention_decode_tma: chunk=%d must be a multiple of %d", chunk, BK);
@@ -553,6 +572,7 @@ MI_API int mi_attention_decode_tma(void* out, const void* q_base, int q_stride, 
   a.max_splits = max_splits;
   a.gp = G < 16 ? G : 16;
   a.scale = scale;
+  a.sink = sink; a.gate = (const __nv_bfloat16*)gate; a.gate_stride = gate_stride;
   int stages = MAX_STAGES;
   while (stages > CONSUMERS && smem_bytes(stages, a.gp, max_splits, n_dec) > 220 * 1024) stages -= CONSUMERS;
   MI_REQUIRE(smem_bytes(stages, a.gp, max_splits, n_dec) <= 227 * 1024, "attention_decode_tma: shared memory does not suffice");
@@ -580,7 +600,8 @@ MI_API int mi_attention_decode_tma(void* out, const void* q_base, int q_stride, 
 MI_API int mi_attention_decode_tma_supported() { return 0; }
 MI_API int mi_kv_tensor_map(void*, const void*, long long) { return mi_fail("kv_tensor_map: head size %d has no TMA kernel", MI_HEAD_DIM); }
 MI_API int mi_attention_decode_tma(void*, const void*, int, const void*, const int*, int, const int*, const int*, const int*,
-                                   const int*, float*, int*, int*, int, int, int, int, float, int, int, int, int, cudaStream_t) {
+                                   const int*, float*, int*, int*, int, int, int, int, float, int, int, int, int, cudaStream_t,
+                                   const float*, const void*, int) {
   return mi_fail("attention_decode_tma: head size %d has no TMA kernel", MI_HEAD_DIM);
 }
 

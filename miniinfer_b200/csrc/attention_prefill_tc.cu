@@ -143,6 +143,14 @@ constexpr int OUT_ROW_BYTES = HD;                       // a softmax thread's ha
 constexpr size_t SMEM_BYTES = 1024 + Q_BYTES + KV_RING_BYTES + 256 + (2 * STREAMS * TPR + 2 * STREAMS * (TPR + 1)) * BM * sizeof(float) +
                               (size_t)SOFTMAX_WARPS * 32 * OUT_ROW_BYTES;
 
+// two bf16 outputs times the sigmoid of two bf16 gate logits
+__device__ __forceinline__ uint32_t gate_pair(uint32_t o2, uint32_t g2) {
+  const float2 o = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&o2));
+  const float2 g = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&g2));
+  const __nv_bfloat162 r = __floats2bfloat162_rn(__fdividef(o.x, 1.f + __expf(-g.x)), __fdividef(o.y, 1.f + __expf(-g.y)));
+  return *reinterpret_cast<const uint32_t*>(&r);
+}
+
 struct Args {
   __nv_bfloat16* out;            // [T, nh * HD]
   const int* block_table;
@@ -158,6 +166,9 @@ struct Args {
   int hw;                        // query heads of a work: hpt, or 2 x hpt when a pair of blocks shares the work
   int skip_odd;                  // hpt = 1 on a list of 64-token tiles: the tiles that start at an odd multiple of 64 are covered by the tile before
   float scale_log2;              // scale * log2(e)
+  const float* sink;             // [nh] or null: a logit per query head whose exponential joins the denominator once
+  const __nv_bfloat16* gate;     // [T, gate_stride] or null: the output is multiplied with sigmoid(gate[token, head * HD + d])
+  int gate_stride;
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -753,10 +764,11 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __g
       asm volatile("bar.sync 9, %0;" ::"n"(SOFTMAX_WARPS * 32) : "memory");
       tc_fence_after();
       const float m0 = fm[r], m1 = fm[BM + r];
-      const float m_all = fmaxf(m0, m1);
+      const float sink2 = a.sink ? a.sink[head] * 1.4426950408889634f : -INFINITY;   // base 2, like the scores
+      const float m_all = fmaxf(fmaxf(m0, m1), sink2);
       const float w0 = m0 == -INFINITY ? 0.f : exp2f(m0 - m_all);
       const float w1 = m1 == -INFINITY ? 0.f : exp2f(m1 - m_all);
-      const float l_all = fl[r] * w0 + fl[BM + r] * w1;
+      const float l_all = fl[r] * w0 + fl[BM + r] * w1 + (a.sink ? exp2f(sink2 - m_all) : 0.f);
       constexpr int OD = HD / 2;                           // output columns of this thread
       const bool has1 = n > 1;
       const float f0 = w0 / l_all, f1 = has1 ? w1 / l_all : 0.f;
@@ -793,7 +805,11 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __g
           const int tok2 = a.hpt == 2 ? (rg & 63) : rg;
           const int head2 = wk.head0 + (a.hpt == 2 ? (rg >> 6) : 0);
           if (tok2 < rows_tok) {
-            const uint4 wv = *reinterpret_cast<const uint4*>(mine + rw * OUT_ROW_BYTES + ((chunk ^ (rw & (CH - 1))) << 4));
+            uint4 wv = *reinterpret_cast<const uint4*>(mine + rw * OUT_ROW_BYTES + ((chunk ^ (rw & (CH - 1))) << 4));
+            if (a.gate) {
+              const uint4 gv = *reinterpret_cast<const uint4*>(a.gate + (size_t)(wk.row0 + tok2) * a.gate_stride + (size_t)head2 * HD + st * OD + chunk * 8);
+              wv.x = gate_pair(wv.x, gv.x); wv.y = gate_pair(wv.y, gv.y); wv.z = gate_pair(wv.z, gv.z); wv.w = gate_pair(wv.w, gv.w);
+            }
             *reinterpret_cast<uint4*>(a.out + (size_t)(wk.row0 + tok2) * a.nh * HD + (size_t)head2 * HD + st * OD + chunk * 8) = wv;
           }
         }
@@ -917,8 +933,10 @@ int launch_prefill_tc(const CUtensorMap& qm, const CUtensorMap& km, const Args& 
 MI_API int mi_attention_prefill_tc(void* out, const void* q_map, const void* kv_map, const int* block_table, int bt_stride,
                                    const int* tiles, int n_tiles, const int* q_start, const int* q_len, const int* ctx_len,
                                    const int* seq_slot, int* status, int nh, int nkv, int page_size, float scale, int window,
-                                   int num_sms, cudaStream_t stream, const int* tiles128, int n_tiles128, int pairs) {
+                                   int num_sms, cudaStream_t stream, const int* tiles128, int n_tiles128, int pairs,
+                                   const float* sink, const void* gate, int gate_stride) {
   MI_REQUIRE(num_sms > 0, "attention_prefill_tc: num_sms");
+  MI_REQUIRE(gate == nullptr || (((uintptr_t)gate % 16) == 0 && gate_stride % 8 == 0), "attention_prefill_tc: the gate rows must be 16-byte aligned");
   MI_REQUIRE(n_tiles >= 0 && nh > 0 && nkv > 0 && nh % nkv == 0, "attention_prefill_tc: bad head counts nh=%d nkv=%d", nh, nkv);
   MI_REQUIRE(page_size % 64 == 0, "attention_prefill_tc: page_size=%d must be a multiple of 64", page_size);
   MI_REQUIRE(scale > 0.f, "attention_prefill_tc: the scale must be positive");
@@ -936,6 +954,7 @@ MI_API int mi_attention_prefill_tc(void* out, const void* q_map, const void* kv_
   a.status = status;
   a.n_tiles = n_tiles; a.nh = nh; a.nkv = nkv; a.page_size = page_size; a.window = window;
   a.scale_log2 = scale * 1.4426950408889634f;
+  a.sink = sink; a.gate = (const __nv_bfloat16*)gate; a.gate_stride = gate_stride;
   CUtensorMap qm, km;
   memcpy(&qm, q_map, sizeof(qm));
   memcpy(&km, kv_map, sizeof(km));
@@ -973,7 +992,8 @@ MI_API int mi_attention_prefill_tc(void* out, const void* q_map, const void* kv_
 MI_API int mi_attention_prefill_tc_supported() { return 0; }
 MI_API int mi_qkv_tensor_map(void*, const void*, long long, long long) { return mi_fail("qkv_tensor_map: head size %d has no tcgen05 kernel", MI_HEAD_DIM); }
 MI_API int mi_attention_prefill_tc(void*, const void*, const void*, const int*, int, const int*, int, const int*, const int*, const int*,
-                                   const int*, int*, int, int, int, float, int, int, cudaStream_t, const int*, int, int) {
+                                   const int*, int*, int, int, int, float, int, int, cudaStream_t, const int*, int, int,
+                                   const float*, const void*, int) {
   return mi_fail("attention_prefill_tc: head size %d has no tcgen05 kernel", MI_HEAD_DIM);
 }
 

@@ -71,6 +71,11 @@ struct Args {
   int K, ldo;
   int second;            // row of w where the second box of a tile starts, relative to the first (SwiGLU: I; plain: 128)
   int tiles_m, tiles_n;
+  // Grouped product (null: one matrix for all rows): the rows come sorted by expert, every expert's rows starting at a
+  // multiple of tile_rows; tile_expert[row / tile_rows] is the expert whose matrix - rows expert * expert_rows .. of w -
+  // those rows are multiplied with, or -1 for rows nobody owns (such tiles are passed over by all three roles alike).
+  const int* tile_expert;
+  int tile_rows, expert_rows;
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -268,7 +273,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constant_
       uint32_t ready = mbar_peek(&empty[0], 1);
       for (int tile = first_tile; tile < n_tiles && !*abort; tile += tile_step) {
         const int tm = tile % tiles_m, tn = tile / tiles_m;
-        const int row0 = (tm * CTAS + rank) * BM, n0 = tn * TILE_COLS;
+        int w0 = 0;
+        if (a.tile_expert) {
+          const int e = a.tile_expert[(tm * CTAS * BM) / a.tile_rows];
+          if (e < 0) continue;
+          w0 = e * a.expert_rows;
+        }
+        const int row0 = (tm * CTAS + rank) * BM, n0 = w0 + tn * TILE_COLS;
         for (int kb = 0; kb < kblocks; ++kb, ++it) {
           const int s = it % STAGES;
           if (!ready) {
@@ -303,7 +314,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constant_
       // is needed in the loop.)
       int it = 0, t = 0;
       uint32_t ready = 0;
-      for (int tile = first_tile; tile < n_tiles && !*abort; tile += tile_step, ++t) {
+      for (int tile = first_tile; tile < n_tiles && !*abort; tile += tile_step) {
+        if (a.tile_expert && a.tile_expert[((tile % tiles_m) * CTAS * BM) / a.tile_rows] < 0) continue;
         const int buf = t & 1;
         mbar_wait(&acc_empty[buf], ((t >> 1) & 1) ^ 1, abort, a.status);
         tc_fence_after();
@@ -324,14 +336,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constant_
           tc_commit<CTAS>(&empty[s]);
         }
         tc_commit<CTAS>(&acc_full[buf]);
+        ++t;
       }
     }
     __syncwarp();
   } else {
     // ---------------------------------------------------------------- epilogue warps 0..3
     int t = 0;
-    for (int tile = first_tile; tile < n_tiles; tile += tile_step, ++t) {
+    for (int tile = first_tile; tile < n_tiles; tile += tile_step) {
       const int tm = tile % tiles_m, tn = tile / tiles_m;
+      if (a.tile_expert && a.tile_expert[(tm * CTAS * BM) / a.tile_rows] < 0) continue;
       const int buf = t & 1;
       mbar_wait(&acc_full[buf], (t >> 1) & 1, abort, a.status);
       if (*abort) break;
@@ -372,6 +386,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constant_
               *reinterpret_cast<uint4*>(orow + col + q * 8) = make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
         }
       }
+      ++t;
     }
   }
   tc_fence_before();
@@ -468,15 +483,19 @@ int launch_tc(const CUtensorMap& xm, const CUtensorMap& wm, const Args& a, int s
 }
 
 template <bool SWIGLU>
-int run(void* out, const void* x, const void* w, int M, int N, int K, int ldo, int* status, int pairs, cudaStream_t stream) {
-  // N: output columns; w has N rows (plain) or 2 N rows (SwiGLU)
+int run(void* out, const void* x, const void* w, int M, int N, int K, int ldo, int* status, int pairs, cudaStream_t stream,
+        int experts = 1, const int* tile_expert = nullptr, int tile_rows = 0) {
+  // N: output columns; w has N rows (plain) or 2 N rows (SwiGLU), per expert
   MI_REQUIRE(M > 0 && N > 0 && K >= BK && K % 8 == 0 && N % 8 == 0 && ldo % 8 == 0 && ldo >= N,
              "gemm_tc: M=%d N=%d K=%d ldo=%d: K (at least 64), N and the row stride must be multiples of 8", M, N, K, ldo);
   MI_REQUIRE(((uintptr_t)x % 16) == 0 && ((uintptr_t)w % 16) == 0 && ((uintptr_t)out % 16) == 0, "gemm_tc: operands must be 16-byte aligned");
   CUtensorMap xm, wm;
   if (int e = encode_map(&xm, x, M, K)) return e;
-  if (int e = encode_map(&wm, w, SWIGLU ? 2LL * N : (long long)N, K)) return e;
+  if (int e = encode_map(&wm, w, (long long)experts * (SWIGLU ? 2LL * N : (long long)N), K)) return e;
   Args a;
+  a.tile_expert = tile_expert;
+  a.tile_rows = tile_rows;
+  a.expert_rows = SWIGLU ? 2 * N : N;
   a.out = (__nv_bfloat16*)out;
   a.status = status;
   a.M = M; a.N = N; a.K = K; a.ldo = ldo;
@@ -505,6 +524,17 @@ int run(void* out, const void* x, const void* w, int M, int N, int K, int ldo, i
 MI_API int mi_gemm_tc_swiglu_bf16(void* out, const void* x, const void* w, int M, int I, int K, int ldo, int* status,
                                   int pairs, cudaStream_t stream) {
   return run<true>(out, x, w, M, I, K, ldo, status, pairs, stream);
+}
+
+// The grouped form: x [M, K] holds rows sorted by expert, every expert's rows starting at a multiple of tile_rows (a
+// multiple of 256); tile_expert [M / tile_rows] (device) names the expert of each stretch, -1 where nobody owns the rows;
+// w stacks the experts' matrices ([experts, 2 N, K] with SwiGLU, gate rows then up rows; [experts, N, K] without).
+MI_API int mi_gemm_tc_grouped_bf16(void* out, const void* x, const void* w, int M, int N, int K, int ldo, int experts, int swiglu,
+                                   const int* tile_expert, int tile_rows, int* status, int pairs, cudaStream_t stream) {
+  MI_REQUIRE(experts > 0 && tile_expert != nullptr && tile_rows > 0 && tile_rows % 256 == 0 && M % tile_rows == 0,
+             "gemm_tc_grouped: rows=%d must come in stretches of tile_rows=%d, a multiple of 256", M, tile_rows);
+  return swiglu ? run<true>(out, x, w, M, N, K, ldo, status, pairs, stream, experts, tile_expert, tile_rows)
+                : run<false>(out, x, w, M, N, K, ldo, status, pairs, stream, experts, tile_expert, tile_rows);
 }
 
 // out[M, N] = x w^T, all bf16.

@@ -1,7 +1,7 @@
 // Routed experts (a mixture of small SwiGLU feed-forward layers of which each token uses `top`), in
 // five kernels and without a word read back by the host, so that a step can be recorded as a graph:
 //
-//   route    one warp per token: logits z = W_router h in float32 (W_router is kept in float32), scores
+//   route    one block per token: logits z = W_router h in float32 (W_router is kept in float32), scores
 //            s = sigmoid(z), choice = s + correction; the `top` experts of largest choice (ties: the lower
 //            index); weights = their s divided by (the sum of those s + 1e-20).
 //   align    one block: counts the (token, choice) pairs of every expert, gives each expert a range of
@@ -21,38 +21,48 @@
 namespace {
 
 constexpr int MAX_EXPERTS = 256;
-constexpr int ROUTE_WARPS = 4;
+constexpr int ROUTE_WARPS = 8;
 
+// A block per token; its warps take the experts in turn (a warp sums one expert's logit over the row, eight values a lane
+// in flight), then the first warp picks the `top` choices.  The order of every sum depends on H alone.
 template <typename T>
 __global__ void __launch_bounds__(ROUTE_WARPS * 32)
 moe_route_kernel(const T* __restrict__ x, int Tn, int H, const float* __restrict__ wr, const float* __restrict__ corr,
                  int E, int top, int* __restrict__ idx_out, float* __restrict__ w_out) {
-  __shared__ float s_score[ROUTE_WARPS][MAX_EXPERTS];
-  __shared__ float s_choice[ROUTE_WARPS][MAX_EXPERTS];
+  __shared__ float s_score[MAX_EXPERTS];
+  __shared__ float s_choice[MAX_EXPERTS];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int t = blockIdx.x * ROUTE_WARPS + warp;
+  const int t = blockIdx.x;
   mi::grid_dependency_sync();
-  if (t >= Tn) return;
   const T* row = x + (size_t)t * H;
-  for (int e = 0; e < E; ++e) {
+  for (int e = warp; e < E; e += ROUTE_WARPS) {
     const float* w = wr + (size_t)e * H;
-    float acc = 0.f;
-    for (int h = lane; h < H; h += 32) acc = fmaf(w[h], mi::to_float(row[h]), acc);
+    float part[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) part[i] = 0.f;
+    int h = lane;
+    for (; h + 7 * 32 < H; h += 8 * 32) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) part[i] = fmaf(w[h + 32 * i], mi::to_float(row[h + 32 * i]), part[i]);
+    }
+    for (int i = 0; h < H; h += 32, ++i) part[i] = fmaf(w[h], mi::to_float(row[h]), part[i]);
+    float acc = ((part[0] + part[1]) + (part[2] + part[3])) + ((part[4] + part[5]) + (part[6] + part[7]));
     acc = mi::warp_sum(acc);
     if (lane == 0) {
       const float s = 1.f / (1.f + expf(-acc));
-      s_score[warp][e] = s;
-      s_choice[warp][e] = s + corr[e];
+      s_score[e] = s;
+      s_choice[e] = s + corr[e];
     }
   }
-  __syncwarp();
+  __syncthreads();
+  if (warp != 0) return;
   float sum = 0.f;
   float mine = 0.f;   // lane k keeps the score of choice k
   for (int k = 0; k < top; ++k) {
     float best = -INFINITY;
     int bi = 0x7fffffff;
     for (int e = lane; e < E; e += 32) {
-      const float c = s_choice[warp][e];
+      const float c = s_choice[e];
       if (c > best) { best = c; bi = e; }     // within a lane indices grow, so the first of equals stays
     }
 #pragma unroll
@@ -61,12 +71,12 @@ moe_route_kernel(const T* __restrict__ x, int Tn, int H, const float* __restrict
       const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
       if (ob > best || (ob == best && oi < bi)) { best = ob; bi = oi; }
     }
-    const float s = s_score[warp][bi];
+    const float s = s_score[bi];
     sum += s;
     if (lane == k) mine = s;
     if (lane == 0) {
       idx_out[(size_t)t * top + k] = bi;
-      s_choice[warp][bi] = -INFINITY;
+      s_choice[bi] = -INFINITY;
     }
     __syncwarp();
   }
@@ -346,17 +356,30 @@ moe_gemm_f32_kernel(GroupedArgs a) {
   }
 }
 
-template <typename TOut>
+template <typename TOut, typename TY>
 __global__ void __launch_bounds__(256)
-moe_combine_kernel(TOut* __restrict__ out, const float* __restrict__ y, const int* __restrict__ pos_of,
+moe_combine_kernel(TOut* __restrict__ out, const TY* __restrict__ y, const int* __restrict__ pos_of,
                    const float* __restrict__ w, int top, int N) {
   mi::grid_dependency_sync();
   const int t = blockIdx.x;
   for (int n = threadIdx.x; n < N; n += blockDim.x) {
     float acc = 0.f;
-    for (int k = 0; k < top; ++k) acc = fmaf(w[(size_t)t * top + k], y[(size_t)pos_of[(size_t)t * top + k] * N + n], acc);
+    for (int k = 0; k < top; ++k) acc = fmaf(w[(size_t)t * top + k], mi::to_float(y[(size_t)pos_of[(size_t)t * top + k] * N + n]), acc);
     out[(size_t)t * N + n] = mi::from_float<TOut>(acc);
   }
+}
+
+// The tokens' rows put in the order of the experts' rows: xs[pos] = x[pair / top] for the rows that a pair owns, zeros
+// for the others; 16 bytes a thread.  (The tcgen05 product reads its rows by TMA, which wants them side by side.)
+__global__ void __launch_bounds__(256)
+moe_gather_kernel(__nv_bfloat16* __restrict__ xs, const __nv_bfloat16* __restrict__ x, const int* __restrict__ sorted_pair,
+                  int top, int H8) {
+  mi::grid_dependency_sync();
+  const int pos = blockIdx.x;
+  const int pair = sorted_pair[pos];
+  uint4* dst = reinterpret_cast<uint4*>(xs) + (size_t)pos * H8;
+  const uint4* src = pair >= 0 ? reinterpret_cast<const uint4*>(x) + (size_t)(pair / top) * H8 : nullptr;
+  for (int i = threadIdx.x; i < H8; i += blockDim.x) dst[i] = src ? src[i] : make_uint4(0, 0, 0, 0);
 }
 
 template <int WM, int WN, bool SWIGLU>
@@ -386,7 +409,7 @@ MI_API int mi_moe_route(const void* x, int dtype, int T, int H, const float* rou
   MI_REQUIRE(T >= 0 && H > 0 && E > 0 && E <= MAX_EXPERTS, "moe_route: experts=%d must lie in 1..%d", E, MAX_EXPERTS);
   MI_REQUIRE(top > 0 && top <= E && top <= 32, "moe_route: top=%d must lie in 1..min(experts, 32)", top);
   if (T == 0) return 0;
-  const dim3 grid((T + ROUTE_WARPS - 1) / ROUTE_WARPS);
+  const dim3 grid(T);
   if (dtype == MI_BF16)
     mi::launch(moe_route_kernel<__nv_bfloat16>, grid, dim3(ROUTE_WARPS * 32), 0, stream, (const __nv_bfloat16*)x, T, H, router, correction, E, top, idx_out, w_out);
   else if (dtype == MI_F32)
@@ -440,16 +463,28 @@ MI_API int mi_moe_gemm(const void* a_rows, int dtype, int a_stride, const void* 
   return 0;
 }
 
-MI_API int mi_moe_combine(void* out, int out_dtype, const float* y, const int* pos_of, const float* weights, int T, int top, int N,
+MI_API int mi_moe_gather(void* xs, const void* x, const int* sorted_pair, int rows, int top, int H, cudaStream_t stream) {
+  MI_REQUIRE(rows >= 0 && top > 0 && H > 0 && H % 8 == 0, "moe_gather: rows of %d values (a multiple of 8 in bfloat16)", H);
+  MI_REQUIRE(((uintptr_t)xs % 16) == 0 && ((uintptr_t)x % 16) == 0, "moe_gather: operands must be 16-byte aligned");
+  if (rows == 0) return 0;
+  mi::launch(moe_gather_kernel, dim3(rows), dim3(256), 0, stream, (__nv_bfloat16*)xs, (const __nv_bfloat16*)x, sorted_pair, top, H / 8);
+  MI_LAUNCH_OK("moe_gather");
+  return 0;
+}
+
+// y: the down rows, float32 (y_dtype MI_F32) or bfloat16
+MI_API int mi_moe_combine(void* out, int out_dtype, const void* y, int y_dtype, const int* pos_of, const float* weights, int T, int top, int N,
                           cudaStream_t stream) {
   MI_REQUIRE(T >= 0 && top > 0 && N > 0, "moe_combine: bad sizes");
   if (T == 0) return 0;
-  if (out_dtype == MI_BF16)
-    mi::launch(moe_combine_kernel<__nv_bfloat16>, dim3(T), dim3(256), 0, stream, (__nv_bfloat16*)out, y, pos_of, weights, top, N);
-  else if (out_dtype == MI_F32)
-    mi::launch(moe_combine_kernel<float>, dim3(T), dim3(256), 0, stream, (float*)out, y, pos_of, weights, top, N);
+  if (out_dtype == MI_BF16 && y_dtype == MI_F32)
+    mi::launch(moe_combine_kernel<__nv_bfloat16, float>, dim3(T), dim3(256), 0, stream, (__nv_bfloat16*)out, (const float*)y, pos_of, weights, top, N);
+  else if (out_dtype == MI_BF16 && y_dtype == MI_BF16)
+    mi::launch(moe_combine_kernel<__nv_bfloat16, __nv_bfloat16>, dim3(T), dim3(256), 0, stream, (__nv_bfloat16*)out, (const __nv_bfloat16*)y, pos_of, weights, top, N);
+  else if (out_dtype == MI_F32 && y_dtype == MI_F32)
+    mi::launch(moe_combine_kernel<float, float>, dim3(T), dim3(256), 0, stream, (float*)out, (const float*)y, pos_of, weights, top, N);
   else
-    return mi_fail("moe_combine: unknown dtype %d", out_dtype);
+    return mi_fail("moe_combine: unknown dtypes %d, %d", out_dtype, y_dtype);
   MI_LAUNCH_OK("moe_combine");
   return 0;
 }

@@ -415,6 +415,10 @@ def qkv_norm_mix_store(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, q
     _ptr(kv_layer) if kv_layer is not None else none, page_size, _stream()))
 
 
+MOE_TC_ROW_TILE = 256            # rows of a stretch of the tcgen05 grouped product: what a pair of blocks takes at a time
+MOE_TC_MIN_ROWS_PER_EXPERT = 128   # from this many (token, choice) pairs per expert on, on average, the tcgen05 product runs
+
+
 def moe_row_tile(num_pairs: int, num_experts: int, dtype: torch.dtype) -> int:
   """Rows of a row tile of the grouped products for a step with ``num_pairs`` (token, choice) pairs."""
   return int(common_lib().mi_moe_row_tile(num_pairs, num_experts, F32 if dtype == torch.float32 else BF16))
@@ -445,7 +449,12 @@ def routed_experts(out: torch.Tensor, x: torch.Tensor, router: torch.Tensor, cor
   if T == 0:
     return
   pairs = T * top
-  tile = moe_row_tile(pairs, E, x.dtype)
+  # Many rows per expert in bfloat16: the products on tcgen05 (gemm_tc.cu in its grouped form) over rows gathered into the
+  # experts' order, every expert's rows starting at a multiple of 256.  Otherwise the mma.sync / FMA kernels of moe.cu,
+  # which gather as they load and take row tiles of 16 or 64.
+  on_tc = (x.dtype == torch.bfloat16 and pairs >= MOE_TC_MIN_ROWS_PER_EXPERT * E and H >= 64 and ff >= 64 and H % 8 == 0 and ff % 8 == 0
+           and os.environ.get("MINIINFER_B200_MOE_TC", "1") != "0")
+  tile = MOE_TC_ROW_TILE if on_tc else moe_row_tile(pairs, E, x.dtype)
   rows = moe_rows(pairs, E, tile)
   tiles = rows // tile
   idx = workspace.buffer("moe_choice", (pairs,), torch.int32)
@@ -454,14 +463,25 @@ def routed_experts(out: torch.Tensor, x: torch.Tensor, router: torch.Tensor, cor
   pos_of = workspace.buffer("moe_pos", (pairs,), torch.int32)
   tile_expert = workspace.buffer("moe_tile_expert", (tiles,), torch.int32)
   act = workspace.buffer("moe_act", (rows, ff), x.dtype)
-  y = workspace.buffer("moe_y", (rows, H), torch.float32)
+  y = None if on_tc else workspace.buffer("moe_y", (rows, H), torch.float32)
   dt, st = _dt(x), _stream()
   _check(lib, lib.mi_moe_route(_ptr(x), dt, T, H, _ptr(router, torch.float32), _ptr(correction, torch.float32), E, top,
                                _ptr(idx), _ptr(wts), st))
   _check(lib, lib.mi_moe_align(_ptr(idx), pairs, E, tile, _ptr(sorted_pair), _ptr(pos_of), _ptr(tile_expert), rows, tiles, st))
+  if on_tc:
+    xs = workspace.buffer("moe_rows", (rows, H), x.dtype)
+    y16 = workspace.buffer("moe_y16", (rows, H), x.dtype)
+    status = workspace.zeros("gemm_tc_status", 1, torch.int32)
+    _check(lib, lib.mi_moe_gather(_ptr(xs), _ptr(x), _ptr(sorted_pair), rows, top, H, st))
+    _check(lib, lib.mi_gemm_tc_grouped_bf16(_ptr(act), _ptr(xs), _ptr(gate_up), rows, ff, H, ff, E, 1, _ptr(tile_expert), tile,
+                                            _ptr(status, torch.int32), _tc_pairs(), st))
+    _check(lib, lib.mi_gemm_tc_grouped_bf16(_ptr(y16), _ptr(act), _ptr(down), rows, H, ff, H, E, 0, _ptr(tile_expert), tile,
+                                            _ptr(status, torch.int32), _tc_pairs(), st))
+    _check(lib, lib.mi_moe_combine(_ptr(out), _dt(out), _ptr(y16), BF16, _ptr(pos_of), _ptr(wts), T, top, H, st))
+    return
   _check(lib, lib.mi_moe_gemm(_ptr(x), dt, H, _ptr(gate_up), _ptr(act), _ptr(sorted_pair), _ptr(tile_expert), tiles, tile, ff, H, top, 1, st))
   _check(lib, lib.mi_moe_gemm(_ptr(act), dt, ff, _ptr(down), _ptr(y), _ptr(sorted_pair), _ptr(tile_expert), tiles, tile, H, ff, top, 0, st))
-  _check(lib, lib.mi_moe_combine(_ptr(out), _dt(out), _ptr(y), _ptr(pos_of), _ptr(wts), T, top, H, st))
+  _check(lib, lib.mi_moe_combine(_ptr(out), _dt(out), _ptr(y), F32, _ptr(pos_of), _ptr(wts), T, top, H, st))
 
 
 def linear_swiglu(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, workspace, force_skinny: bool = False,
@@ -745,9 +765,11 @@ def _attention_bf16(out, qkv, kv_layer, block_table, batch, nh, nkv, hd, scale, 
   lib = attention_lib(hd)
   if opts is None:
     opts = _AttentionOptions(None, None, 0, 0, hd)
-  plain = opts.plain(hd)      # the TMA / tcgen05 kernels take neither sink nor gate nor a narrower output
+  whole_heads = opts.out_hd == hd      # the TMA and tcgen05 kernels write whole heads; sink and gate they take
   if batch.num_prefill_tiles:
-    use_tc = (plain and page_size % 64 == 0 and lib.mi_attention_prefill_tc_supported() == 1
+    # the tcgen05 kernel takes sink and gate; its output rows are whole heads, and it reads the gate 16 bytes at a time
+    gate_ok = opts.gate is None or (opts.gate_offset % 8 == 0 and opts.gate_stride % 8 == 0 and opts.gate.data_ptr() % 16 == 0)
+    use_tc = (opts.out_hd == hd and gate_ok and page_size % 64 == 0 and lib.mi_attention_prefill_tc_supported() == 1
               and os.environ.get("MINIINFER_B200_PREFILL_TC", "1") != "0")
     if use_tc:
       if batch.scratch is not None:
@@ -764,7 +786,8 @@ def _attention_bf16(out, qkv, kv_layer, block_table, batch, nh, nkv, hd, scale, 
         _ptr(batch.prefill_tiles, torch.int32), batch.num_prefill_tiles, _ptr(batch.q_start, torch.int32),
         _ptr(batch.q_len, torch.int32), _ptr(batch.ctx_len, torch.int32), _ptr(batch.seq_slot, torch.int32),
         _ptr(status, torch.int32), nh, nkv, page_size, ctypes.c_float(scale), win, _num_sms(qkv.device), _stream(),
-        _ptr(wide, torch.int32) if wide is not None else _ptr(None), n_wide, pairs))
+        _ptr(wide, torch.int32) if wide is not None else _ptr(None), n_wide, pairs,
+        opts.sink_ptr(), opts.gate_ptr(), opts.gate_stride))
       if batch.scratch is None and int(status[0]) != 0:
         raise KernelError("attention_prefill_tc: a bounded wait on a barrier ran out")
     else:
@@ -776,7 +799,7 @@ def _attention_bf16(out, qkv, kv_layer, block_table, batch, nh, nkv, hd, scale, 
   if batch.num_decode:
     span = min(batch.max_ctx_len, win) if win else batch.max_ctx_len
     G = nh // nkv
-    tma_shapes = plain and hd % 64 == 0 and page_size % 64 == 0 and os.environ.get("MINIINFER_B200_DECODE_TMA", "1") != "0"
+    tma_shapes = whole_heads and hd % 64 == 0 and page_size % 64 == 0 and os.environ.get("MINIINFER_B200_DECODE_TMA", "1") != "0"
     cluster = decode_cluster_size(lib, hd, batch.num_decode, nkv, span) if (tma_shapes and G <= 8) else 0
     if cluster:
       if batch.scratch is not None:
@@ -787,13 +810,13 @@ def _attention_bf16(out, qkv, kv_layer, block_table, batch, nh, nkv, hd, scale, 
         _ptr(out), _ptr(qkv), qkv.shape[1], _kv_tensor_map(lib, kv_layer), _ptr(block_table, torch.int32), block_table.shape[1],
         _ptr(batch.decode_items, torch.int32), _ptr(batch.q_start, torch.int32), _ptr(batch.ctx_len, torch.int32),
         _ptr(batch.seq_slot, torch.int32), _ptr(status, torch.int32), batch.num_decode, nh, nkv, page_size, ctypes.c_float(scale), win,
-        cluster, batch.max_ctx_len, _stream()))
+        cluster, batch.max_ctx_len, _stream(), opts.sink_ptr(), opts.gate_ptr(), opts.gate_stride))
       if batch.scratch is None and int(status[0]) != 0:
         raise KernelError("attention_decode_cluster: a bounded wait on a copy barrier ran out")
       return
     # more than 8 query heads per kv head: the TMA kernel would walk an item's tiles twice and hand a stage back only
     # in the second pass, which cannot work once an item has more tiles than there are stages - the cp.async kernel takes those
-    use_tma = (plain and hd % 64 == 0 and page_size % 64 == 0 and G <= 8 and os.environ.get("MINIINFER_B200_DECODE_TMA", "1") != "0")
+    use_tma = (whole_heads and hd % 64 == 0 and page_size % 64 == 0 and G <= 8 and os.environ.get("MINIINFER_B200_DECODE_TMA", "1") != "0")
     if use_tma:
       # the TMA kernel deals 64-key tiles out evenly; a (request, kv head) is cut into at most as many
       # pieces as it has tiles, and no more than there are blocks
@@ -814,7 +837,8 @@ def _attention_bf16(out, qkv, kv_layer, block_table, batch, nh, nkv, hd, scale, 
         _ptr(out), _ptr(qkv), qkv.shape[1], _kv_tensor_map(lib, kv_layer), _ptr(block_table, torch.int32), block_table.shape[1],
         _ptr(batch.decode_items, torch.int32), _ptr(batch.q_start, torch.int32), _ptr(batch.ctx_len, torch.int32),
         _ptr(batch.seq_slot, torch.int32), _ptr(scratch, torch.float32), _ptr(counters[1:], torch.int32), _ptr(counters[:1], torch.int32),
-        batch.num_decode, nh, nkv, page_size, ctypes.c_float(scale), win, chunk, max_splits, _num_sms(qkv.device), _stream()))
+        batch.num_decode, nh, nkv, page_size, ctypes.c_float(scale), win, chunk, max_splits, _num_sms(qkv.device), _stream(),
+        opts.sink_ptr(), opts.gate_ptr(), opts.gate_stride))
       if batch.scratch is None and int(counters[0]) != 0:
         raise KernelError("attention_decode_tma: a bounded wait on a copy barrier ran out")
     else:

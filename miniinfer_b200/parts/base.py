@@ -53,7 +53,7 @@ class ParamSpec:
   shape: Tuple[int, ...]
   role: str
   sources: List[List[Piece]]
-  init: str = "normal"            # random-weights mode: "normal" (std given by the model), "ones_noise" (about 1) or "half_noise" (about 0.5)
+  init: str = "normal"            # random-weights mode: "normal" (std given by the model), "ones_noise" (about 1), "half_noise" (about 0.5) or "fan_in" (1.5 / sqrt(columns))
 
   def __post_init__(self):
     if self.role not in ("matrix", "table", "vector", "matrix_f32", "int"):

@@ -85,7 +85,7 @@ class RoutedExpertsFeedForward(FeedForward):
     gate_up = [p for e in range(E) for p in (Piece(f"{n}.e{e}.gate", 2 * F * e, (F, H)), Piece(f"{n}.e{e}.up", 2 * F * e + F, (F, H)))]
     down = [Piece(f"{n}.e{e}.down", H * e, (H, F)) for e in range(E)]
     return {
-      "router": ParamSpec((E, H), "matrix_f32", [whole(f"{n}.router", (E, H))]),
+      "router": ParamSpec((E, H), "matrix_f32", [whole(f"{n}.router", (E, H))], init="fan_in"),
       "correction": ParamSpec((E,), "vector", [whole(f"{n}.correction", (E,))]),
       "gate_up": ParamSpec((2 * F * E, H), "matrix", [gate_up]),
       "down": ParamSpec((H * E, F), "matrix", [down]),

@@ -30,6 +30,8 @@ def _draw(shape, init: str, std: float, gen: torch.Generator, device="cpu") -> t
     return 1.0 + NORM_NOISE * t
   if init == "half_noise":
     return 0.5 + NORM_NOISE * t
+  if init == "fan_in":          # logits of about unit size from rows of about unit size: a router that does choose
+    return t * (1.5 / max(1, int(shape[-1])) ** 0.5)
   return std * t
 
 

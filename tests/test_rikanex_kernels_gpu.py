@@ -218,10 +218,12 @@ def test_window_edges_sinks_and_gate(dtype, H, G, D, Dv, window, page):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("T,W,F,E,top", [(5, 72, 40, 5, 2), (1, 64, 24, 3, 1), (300, 72, 40, 5, 2), (700, 128, 48, 16, 4), (33, 96, 56, 6, 6)])
+@pytest.mark.parametrize("T,W,F,E,top", [(5, 72, 40, 5, 2), (1, 64, 24, 3, 1), (300, 72, 40, 5, 2), (700, 128, 48, 16, 4), (33, 96, 56, 6, 6),
+                                         (900, 128, 64, 4, 2), (1100, 192, 136, 6, 3)])
 def test_routed_experts(dtype, T, W, F, E, top):
   """Sigmoid scores, choice by score + correction, weights from the scores alone, the weighted sum of the chosen experts:
-  few tokens (row tiles of 16) and many (tiles of 64), sizes that cut the tiles of the products in both directions."""
+  few tokens (row tiles of 16) and many (tiles of 64; the last two cases: stretches of 256 rows through the tcgen05
+  product in bfloat16), sizes that cut the tiles of the products in both directions."""
   ops = ops_module()
   from miniinfer_b200.engine.context import Workspace
   g = torch.Generator().manual_seed(T + E)
