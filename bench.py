@@ -686,7 +686,7 @@ def _compare_groups(times: dict) -> dict:
   for name, us in times.items():
     if re.search(r"decode_tma_kernel|decode_cluster_kernel|decode_split_kernel|decode_merge|attention_prefill|attention_generic", name):
       g["attention"] += us
-    elif "moe_gemm" in name:
+    elif "moe_gemm" in name or re.search(r"gemm_tc_kernel<\w+, \w+, (true|\(bool\)1)>", name):     # the grouped instantiation of the tcgen05 product
       g["experts"] += us
     elif re.search(r"moe_route|moe_align|moe_combine", name):
       g["routing"] += us
@@ -750,7 +750,16 @@ def compare_one(name: str, cfg: dict, size: dict, batch: int, steps: int, warmup
       attn_bytes = batch * min(CONTEXT, win) * L * 2 * G * hd * 2
       moe_layers = L - 1 if name == "rikanex" else 0
       E, F, top = size["experts"], size["expert_ff"], size["top"]
-      touched = E * (1.0 - (1.0 - top / E) ** batch)             # experts a decode step of `batch` tokens reads, on average
+      touched = E * (1.0 - (1.0 - top / E) ** batch)             # experts a decode step of `batch` tokens reads if choices are uniform
+      if name == "rikanex":
+        # what the last step's last routed layer did read: the row tiles that an expert owns (few rows: a tile an expert)
+        for gph in engine.runner._graphs.values():
+          buf = gph.ws._bufs.get(("moe_tile_expert", torch.int32))
+          if buf is not None:
+            touched = float((buf >= 0).sum().item())
+      for grp in (pk_times, dk):
+        for key in grp:
+          grp[key] = max(grp[key], 1e-9)
       rates = {"prefill_attention": {"us": round(pk_times["attention"], 1), "TFLOP/s": round(attn_flops / pk_times["attention"] / 1e6, 1),
                                      "frac": round(attn_flops / pk_times["attention"] / 1e6 / pk["bf16_tflops"], 4)},
                "decode_attention": {"us": round(dk["attention"], 1), "GB/s": round(attn_bytes / dk["attention"] / 1e3, 1),
@@ -762,6 +771,7 @@ def compare_one(name: str, cfg: dict, size: dict, batch: int, steps: int, warmup
                                     "frac": round(moe_flops / pk_times["experts"] / 1e6 / pk["bf16_tflops"], 4)}
         rates["decode_experts"] = {"us": round(dk["experts"], 1), "GB/s": round(moe_bytes / dk["experts"] / 1e3, 1),
                                    "frac": round(moe_bytes / dk["experts"] / 1e3 / pk["hbm_gbs"], 4)}
+        rates["decode_experts"]["experts_read_per_layer"] = round(touched, 1)
         rates["routing_us"] = {"prefill": round(pk_times["routing"], 1), "decode": round(dk["routing"], 1)}
       dense_ff = (L - moe_layers) * 3 * size["ff"] * W
       proj = L * ((H + 2 * G) * hd * W + W * H * hd + (H * hd * W if name == "rikanex" else 0))

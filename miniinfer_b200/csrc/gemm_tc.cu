@@ -215,7 +215,7 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   return *reinterpret_cast<const uint32_t*>(&v);
 }
 
-template <bool SWIGLU, int CTAS>
+template <bool SWIGLU, int CTAS, bool GROUPED>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constant__ CUtensorMap w_map, Args a) {
   using S = Shape<CTAS>;
@@ -274,7 +274,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constant_
       for (int tile = first_tile; tile < n_tiles && !*abort; tile += tile_step) {
         const int tm = tile % tiles_m, tn = tile / tiles_m;
         int w0 = 0;
-        if (a.tile_expert) {
+        if (GROUPED) {
           const int e = a.tile_expert[(tm * CTAS * BM) / a.tile_rows];
           if (e < 0) continue;
           w0 = e * a.expert_rows;
@@ -315,7 +315,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constant_
       int it = 0, t = 0;
       uint32_t ready = 0;
       for (int tile = first_tile; tile < n_tiles && !*abort; tile += tile_step) {
-        if (a.tile_expert && a.tile_expert[((tile % tiles_m) * CTAS * BM) / a.tile_rows] < 0) continue;
+        if (GROUPED && a.tile_expert[((tile % tiles_m) * CTAS * BM) / a.tile_rows] < 0) continue;
         const int buf = t & 1;
         mbar_wait(&acc_empty[buf], ((t >> 1) & 1) ^ 1, abort, a.status);
         tc_fence_after();
@@ -345,7 +345,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constant_
     int t = 0;
     for (int tile = first_tile; tile < n_tiles; tile += tile_step) {
       const int tm = tile % tiles_m, tn = tile / tiles_m;
-      if (a.tile_expert && a.tile_expert[(tm * CTAS * BM) / a.tile_rows] < 0) continue;
+      if (GROUPED && a.tile_expert[(tm * CTAS * BM) / a.tile_rows] < 0) continue;
       const int buf = t & 1;
       mbar_wait(&acc_full[buf], (t >> 1) & 1, abort, a.status);
       if (*abort) break;
@@ -426,10 +426,10 @@ int encode_map(CUtensorMap* map, const void* base, long long rows, long long col
   return 0;
 }
 
-template <bool SWIGLU, int CTAS>
+template <bool SWIGLU, int CTAS, bool GROUPED>
 int launch_tc(const CUtensorMap& xm, const CUtensorMap& wm, const Args& a, int sms, cudaStream_t stream, bool* placed) {
   using S = Shape<CTAS>;
-  auto kernel = gemm_tc_kernel<SWIGLU, CTAS>;
+  auto kernel = gemm_tc_kernel<SWIGLU, CTAS, GROUPED>;
   static bool configured = false;
   if (!configured) {
     cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)S::SMEM_BYTES);
@@ -482,7 +482,7 @@ int launch_tc(const CUtensorMap& xm, const CUtensorMap& wm, const Args& a, int s
   return 0;
 }
 
-template <bool SWIGLU>
+template <bool SWIGLU, bool GROUPED = false>
 int run(void* out, const void* x, const void* w, int M, int N, int K, int ldo, int* status, int pairs, cudaStream_t stream,
         int experts = 1, const int* tile_expert = nullptr, int tile_rows = 0) {
   // N: output columns; w has N rows (plain) or 2 N rows (SwiGLU), per expert
@@ -509,10 +509,10 @@ int run(void* out, const void* x, const void* w, int M, int N, int K, int ldo, i
   if (sms < 2) pairs = 0;
   bool placed = false;
   if (pairs) {
-    if (int e = launch_tc<SWIGLU, 2>(xm, wm, a, sms, stream, &placed)) return e;
+    if (int e = launch_tc<SWIGLU, 2, GROUPED>(xm, wm, a, sms, stream, &placed)) return e;
   }
   if (!placed) {
-    if (int e = launch_tc<SWIGLU, 1>(xm, wm, a, sms > 0 ? sms : 1, stream, &placed)) return e;
+    if (int e = launch_tc<SWIGLU, 1, GROUPED>(xm, wm, a, sms > 0 ? sms : 1, stream, &placed)) return e;
   }
   return 0;
 }
@@ -533,8 +533,8 @@ MI_API int mi_gemm_tc_grouped_bf16(void* out, const void* x, const void* w, int 
                                    const int* tile_expert, int tile_rows, int* status, int pairs, cudaStream_t stream) {
   MI_REQUIRE(experts > 0 && tile_expert != nullptr && tile_rows > 0 && tile_rows % 256 == 0 && M % tile_rows == 0,
              "gemm_tc_grouped: rows=%d must come in stretches of tile_rows=%d, a multiple of 256", M, tile_rows);
-  return swiglu ? run<true>(out, x, w, M, N, K, ldo, status, pairs, stream, experts, tile_expert, tile_rows)
-                : run<false>(out, x, w, M, N, K, ldo, status, pairs, stream, experts, tile_expert, tile_rows);
+  return swiglu ? run<true, true>(out, x, w, M, N, K, ldo, status, pairs, stream, experts, tile_expert, tile_rows)
+                : run<false, true>(out, x, w, M, N, K, ldo, status, pairs, stream, experts, tile_expert, tile_rows);
 }
 
 // out[M, N] = x w^T, all bf16.

@@ -1,7 +1,8 @@
 // Routed experts (a mixture of small SwiGLU feed-forward layers of which each token uses `top`), in
-// five kernels and without a word read back by the host, so that a step can be recorded as a graph:
+// a product and five kernels, without a word read back by the host, so that a step can be recorded as a graph:
 //
-//   route    one block per token: logits z = W_router h in float32 (W_router is kept in float32), scores
+//   route    (the logits z = W_router h come from the engine's matrix product, accumulated in float32; bfloat16 operands
+//            multiply exactly in float32, so this is the 32-bit sum of the rounded inputs.)  One warp per token: scores
 //            s = sigmoid(z), choice = s + correction; the `top` experts of largest choice (ties: the lower
 //            index); weights = their s divided by (the sum of those s + 1e-20).
 //   align    one block: counts the (token, choice) pairs of every expert, gives each expert a range of
@@ -23,62 +24,46 @@ namespace {
 constexpr int MAX_EXPERTS = 256;
 constexpr int ROUTE_WARPS = 8;
 
-// A block per token; its warps take the experts in turn (a warp sums one expert's logit over the row, eight values a lane
-// in flight), then the first warp picks the `top` choices.  The order of every sum depends on H alone.
-template <typename T>
+// A warp per token: a lane keeps the scores of the experts lane, lane + 32, ... (up to eight) and the warp picks the
+// `top` largest choices one after the other.
 __global__ void __launch_bounds__(ROUTE_WARPS * 32)
-moe_route_kernel(const T* __restrict__ x, int Tn, int H, const float* __restrict__ wr, const float* __restrict__ corr,
-                 int E, int top, int* __restrict__ idx_out, float* __restrict__ w_out) {
-  __shared__ float s_score[MAX_EXPERTS];
-  __shared__ float s_choice[MAX_EXPERTS];
+moe_route_kernel(const float* __restrict__ z, int Tn, const float* __restrict__ corr, int E, int top,
+                 int* __restrict__ idx_out, float* __restrict__ w_out) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int t = blockIdx.x;
+  const int t = blockIdx.x * ROUTE_WARPS + warp;
+  float c_fix[MAX_EXPERTS / 32];
+#pragma unroll
+  for (int i = 0; i < MAX_EXPERTS / 32; ++i) c_fix[i] = lane + 32 * i < E ? corr[lane + 32 * i] : 0.f;   // a weight: fetched before the wait
   mi::grid_dependency_sync();
-  const T* row = x + (size_t)t * H;
-  for (int e = warp; e < E; e += ROUTE_WARPS) {
-    const float* w = wr + (size_t)e * H;
-    float part[8];
+  if (t >= Tn) return;
+  float score[MAX_EXPERTS / 32], choice[MAX_EXPERTS / 32];
 #pragma unroll
-    for (int i = 0; i < 8; ++i) part[i] = 0.f;
-    int h = lane;
-    for (; h + 7 * 32 < H; h += 8 * 32) {
-#pragma unroll
-      for (int i = 0; i < 8; ++i) part[i] = fmaf(w[h + 32 * i], mi::to_float(row[h + 32 * i]), part[i]);
-    }
-    for (int i = 0; h < H; h += 32, ++i) part[i] = fmaf(w[h], mi::to_float(row[h]), part[i]);
-    float acc = ((part[0] + part[1]) + (part[2] + part[3])) + ((part[4] + part[5]) + (part[6] + part[7]));
-    acc = mi::warp_sum(acc);
-    if (lane == 0) {
-      const float s = 1.f / (1.f + expf(-acc));
-      s_score[e] = s;
-      s_choice[e] = s + corr[e];
-    }
+  for (int i = 0; i < MAX_EXPERTS / 32; ++i) {
+    const int e = lane + 32 * i;
+    score[i] = e < E ? 1.f / (1.f + expf(-z[(size_t)t * E + e])) : 0.f;
+    choice[i] = e < E ? score[i] + c_fix[i] : -INFINITY;
   }
-  __syncthreads();
-  if (warp != 0) return;
   float sum = 0.f;
   float mine = 0.f;   // lane k keeps the score of choice k
   for (int k = 0; k < top; ++k) {
-    float best = -INFINITY;
+    float best = -INFINITY, best_s = 0.f;
     int bi = 0x7fffffff;
-    for (int e = lane; e < E; e += 32) {
-      const float c = s_choice[e];
-      if (c > best) { best = c; bi = e; }     // within a lane indices grow, so the first of equals stays
-    }
+#pragma unroll
+    for (int i = 0; i < MAX_EXPERTS / 32; ++i)
+      if (choice[i] > best) { best = choice[i]; bi = lane + 32 * i; best_s = score[i]; }    // indices grow: the first of equals stays
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
       const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+      const float os = __shfl_xor_sync(0xffffffffu, best_s, o);
       const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-      if (ob > best || (ob == best && oi < bi)) { best = ob; bi = oi; }
+      if (ob > best || (ob == best && oi < bi)) { best = ob; bi = oi; best_s = os; }
     }
-    const float s = s_score[bi];
-    sum += s;
-    if (lane == k) mine = s;
-    if (lane == 0) {
-      idx_out[(size_t)t * top + k] = bi;
-      s_choice[bi] = -INFINITY;
-    }
-    __syncwarp();
+    sum += best_s;
+    if (lane == k) mine = best_s;
+    if (lane == 0) idx_out[(size_t)t * top + k] = bi;
+#pragma unroll
+    for (int i = 0; i < MAX_EXPERTS / 32; ++i)
+      if (lane + 32 * i == bi) choice[i] = -INFINITY;
   }
   if (lane < top) w_out[(size_t)t * top + lane] = mine / (sum + 1e-20f);
 }
@@ -404,18 +389,12 @@ MI_API int mi_moe_row_tile(int n_pairs, int E, int dtype) {
   return n_pairs >= 32 * E ? 64 : 16;
 }
 
-MI_API int mi_moe_route(const void* x, int dtype, int T, int H, const float* router, const float* correction, int E, int top,
-                        int* idx_out, float* w_out, cudaStream_t stream) {
-  MI_REQUIRE(T >= 0 && H > 0 && E > 0 && E <= MAX_EXPERTS, "moe_route: experts=%d must lie in 1..%d", E, MAX_EXPERTS);
+// z: the router's logits [T, E] in float32 (a product of the engine's own: W_router h with float32 accumulation)
+MI_API int mi_moe_route(const float* z, int T, const float* correction, int E, int top, int* idx_out, float* w_out, cudaStream_t stream) {
+  MI_REQUIRE(T >= 0 && E > 0 && E <= MAX_EXPERTS, "moe_route: experts=%d must lie in 1..%d", E, MAX_EXPERTS);
   MI_REQUIRE(top > 0 && top <= E && top <= 32, "moe_route: top=%d must lie in 1..min(experts, 32)", top);
   if (T == 0) return 0;
-  const dim3 grid(T);
-  if (dtype == MI_BF16)
-    mi::launch(moe_route_kernel<__nv_bfloat16>, grid, dim3(ROUTE_WARPS * 32), 0, stream, (const __nv_bfloat16*)x, T, H, router, correction, E, top, idx_out, w_out);
-  else if (dtype == MI_F32)
-    mi::launch(moe_route_kernel<float>, grid, dim3(ROUTE_WARPS * 32), 0, stream, (const float*)x, T, H, router, correction, E, top, idx_out, w_out);
-  else
-    return mi_fail("moe_route: unknown dtype %d", dtype);
+  mi::launch(moe_route_kernel, dim3((T + ROUTE_WARPS - 1) / ROUTE_WARPS), dim3(ROUTE_WARPS * 32), 0, stream, z, T, correction, E, top, idx_out, w_out);
   MI_LAUNCH_OK("moe_route");
   return 0;
 }
@@ -436,7 +415,7 @@ MI_API int mi_moe_align(const int* topk_idx, int n_pairs, int E, int TM, int* so
 // swiglu 1: out[row, :N] = silu(a w_gate^T) * (a w_up^T), the expert's matrix holding N gate rows and then N up rows,
 // rows gathered from the tokens; swiglu 0: out[row, :N] = a w^T in float32, rows by position.
 MI_API int mi_moe_gemm(const void* a_rows, int dtype, int a_stride, const void* w, void* out, const int* sorted_pair,
-                       const int* tile_expert, int max_tiles, int TM, int N, int K, int top, int swiglu, cudaStream_t stream) {
+                       const int* tile_expert, int max_tiles, int TM, int N, int K, int top, int swiglu, int busy_tiles, cudaStream_t stream) {
   MI_REQUIRE(N > 0 && K > 0 && max_tiles >= 0 && max_tiles <= 65535, "moe_gemm: bad sizes N=%d K=%d tiles=%d", N, K, max_tiles);
   if (max_tiles == 0) return 0;
   GroupedArgs g;
@@ -453,7 +432,15 @@ MI_API int mi_moe_gemm(const void* a_rows, int dtype, int a_stride, const void* 
     MI_REQUIRE(((uintptr_t)a_rows % 16) == 0 && ((uintptr_t)w % 16) == 0, "moe_gemm: operands must be 16-byte aligned");
     int rc;
     if (TM == 64) rc = swiglu ? launch_bf16<4, 2, true>(g, max_tiles, stream) : launch_bf16<4, 2, false>(g, max_tiles, stream);
-    else if (TM == 16) rc = swiglu ? launch_bf16<1, 4, true>(g, max_tiles, stream) : launch_bf16<1, 4, false>(g, max_tiles, stream);
+    else if (TM == 16) {
+      // few rows an expert: the weights are streamed once, so the columns are cut finely enough to put about two blocks
+      // on every SM (`busy_tiles`: the row tiles that can have rows at all)
+      const int sms = mi::sm_count();
+      const int busy = busy_tiles > 0 && busy_tiles < max_tiles ? busy_tiles : max_tiles;
+      if ((long long)((N + 127) / 128) * busy >= 2LL * sms) rc = swiglu ? launch_bf16<1, 4, true>(g, max_tiles, stream) : launch_bf16<1, 4, false>(g, max_tiles, stream);
+      else if ((long long)((N + 63) / 64) * busy >= 2LL * sms) rc = swiglu ? launch_bf16<1, 2, true>(g, max_tiles, stream) : launch_bf16<1, 2, false>(g, max_tiles, stream);
+      else rc = swiglu ? launch_bf16<1, 1, true>(g, max_tiles, stream) : launch_bf16<1, 1, false>(g, max_tiles, stream);
+    }
     else return mi_fail("moe_gemm: row tiles of 16 or 64 in bfloat16, got %d", TM);
     if (rc) return rc;
   } else {

@@ -12,7 +12,7 @@
 //
 // Key heads have `dim` values and value heads `vdim`; the cache keeps both in rows of `hdp >= max(dim, vdim)`
 // values, so a zero tail adds nothing to a score and its output columns are dropped by the attention
-// kernels (out_hd).  A block per token, the token's heads dealt to its warps.
+// kernels (out_hd).  A warp per (token, head): blocks of four warps, the heads of a token spread over blockIdx.y.
 #include "common.cuh"
 
 namespace {
@@ -49,7 +49,7 @@ qkv_prepare_kernel(PrepArgs<T> a) {
   const T* row = a.proj + (size_t)tkn * a.proj_stride;
   const int units = a.nh + 2 * a.nkv;
   const int page = slot >= 0 ? slot / a.page_size : 0, off = slot >= 0 ? slot % a.page_size : 0;
-  for (int u = warp; u < units; u += PREP_WARPS) {
+  for (int u = blockIdx.y * PREP_WARPS + warp; u < units; u += PREP_WARPS * gridDim.y) {
     if (u < a.nh + a.nkv) {
       // a query head or a key head
       const bool is_q = u < a.nh;
@@ -108,7 +108,7 @@ MI_API int mi_qkv_norm_mix_store(const void* proj, int dtype, int proj_stride, i
                                  int nkv, int dim, int vdim, int hdp, void* q_out, const float* q_w, const float* k_w,
                                  float eps, int normalise, const float* lambda, void* v_other, int v_mode,
                                  const int* slot_mapping, void* kv_layer, int page_size, cudaStream_t stream) {
-  MI_REQUIRE(T >= 0 && nh > 0 && nkv > 0 && dim > 0 && vdim > 0, "qkv_prepare: bad sizes");
+  MI_REQUIRE(T >= 0 && nh > 0 && nkv > 0 && dim > 0 && vdim > 0 && nh + 2 * nkv <= 4 * 65535, "qkv_prepare: bad sizes");
   MI_REQUIRE(hdp >= dim && hdp >= vdim && hdp <= 32 * PREP_MAX_PER_LANE, "qkv_prepare: cache head size %d must cover dim=%d and vdim=%d, up to %d",
              hdp, dim, vdim, 32 * PREP_MAX_PER_LANE);
   MI_REQUIRE(v_mode >= 0 && v_mode <= 2 && (v_mode == 0 || v_other != nullptr) && (v_mode != 2 || lambda != nullptr),
@@ -122,7 +122,7 @@ MI_API int mi_qkv_norm_mix_store(const void* proj, int dtype, int proj_stride, i
     a.nh = nh; a.nkv = nkv; a.dim = dim; a.vdim = vdim; a.hdp = hdp; a.q_out = (TT*)q_out; a.q_w = q_w; a.k_w = k_w; \
     a.eps = eps; a.normalise = normalise; a.lambda = lambda; a.v_other = (TT*)v_other; a.v_mode = v_mode;     \
     a.slot_mapping = slot_mapping; a.kv_layer = (TT*)kv_layer; a.page_size = page_size;                      \
-    mi::launch(qkv_prepare_kernel<TT>, dim3(T), dim3(PREP_WARPS * 32), 0, stream, a);                        \
+    mi::launch(qkv_prepare_kernel<TT>, dim3(T, (nh + 2 * nkv + PREP_WARPS - 1) / PREP_WARPS), dim3(PREP_WARPS * 32), 0, stream, a);                        \
   } while (0)
   if (dtype == MI_BF16) MI_PREP(__nv_bfloat16);
   else if (dtype == MI_F32) MI_PREP(float);

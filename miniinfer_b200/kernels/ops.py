@@ -433,9 +433,10 @@ def routed_experts(out: torch.Tensor, x: torch.Tensor, router: torch.Tensor, cor
                    down: torch.Tensor, top: int, workspace) -> None:
   """out[t] = sum over the ``top`` chosen experts of weight * down_e(silu(gate_e x) * up_e x).
 
-  ``router [E, H]`` and ``correction [E]`` float32: scores sigmoid(router x) in float32; the ``top`` experts of largest
+  ``router [E, H]`` in the rows' dtype and ``correction [E]`` float32: logits ``router x`` accumulated in float32 (bfloat16
+  operands multiply exactly in float32), scores their sigmoid; the ``top`` experts of largest
   score + correction are chosen; weights are their scores divided by the scores' sum (+ 1e-20).  ``gate_up [E, 2 ff, H]``
-  (an expert's gate rows, then its up rows) and ``down [E, H, ff]`` in the rows' dtype.  Five launches, nothing read
+  (an expert's gate rows, then its up rows) and ``down [E, H, ff]`` in the rows' dtype.  Six or seven launches, nothing read
   back by the host; scratch from ``workspace``."""
   lib = common_lib()
   T, H = x.shape
@@ -444,7 +445,7 @@ def routed_experts(out: torch.Tensor, x: torch.Tensor, router: torch.Tensor, cor
   if router.shape != (E, H) or correction.shape != (E,) or gate_up.shape != (E, 2 * ff, H) or down.shape != (E, H, ff) or out.shape != (T, H):
     raise KernelError(f"routed_experts: shapes do not match: x {tuple(x.shape)}, router {tuple(router.shape)}, "
                       f"gate_up {tuple(gate_up.shape)}, down {tuple(down.shape)}")
-  if gate_up.dtype != x.dtype or down.dtype != x.dtype or out.dtype != x.dtype:
+  if gate_up.dtype != x.dtype or down.dtype != x.dtype or out.dtype != x.dtype or router.dtype != x.dtype:
     raise KernelError("routed_experts: rows, experts and out must share a dtype")
   if T == 0:
     return
@@ -465,8 +466,9 @@ def routed_experts(out: torch.Tensor, x: torch.Tensor, router: torch.Tensor, cor
   act = workspace.buffer("moe_act", (rows, ff), x.dtype)
   y = None if on_tc else workspace.buffer("moe_y", (rows, H), torch.float32)
   dt, st = _dt(x), _stream()
-  _check(lib, lib.mi_moe_route(_ptr(x), dt, T, H, _ptr(router, torch.float32), _ptr(correction, torch.float32), E, top,
-                               _ptr(idx), _ptr(wts), st))
+  logits = workspace.buffer("moe_logits", (T, E), torch.float32)
+  linear(logits, x, router)
+  _check(lib, lib.mi_moe_route(_ptr(logits, torch.float32), T, _ptr(correction, torch.float32), E, top, _ptr(idx), _ptr(wts), st))
   _check(lib, lib.mi_moe_align(_ptr(idx), pairs, E, tile, _ptr(sorted_pair), _ptr(pos_of), _ptr(tile_expert), rows, tiles, st))
   if on_tc:
     xs = workspace.buffer("moe_rows", (rows, H), x.dtype)
@@ -479,8 +481,9 @@ def routed_experts(out: torch.Tensor, x: torch.Tensor, router: torch.Tensor, cor
                                             _ptr(status, torch.int32), _tc_pairs(), st))
     _check(lib, lib.mi_moe_combine(_ptr(out), _dt(out), _ptr(y16), BF16, _ptr(pos_of), _ptr(wts), T, top, H, st))
     return
-  _check(lib, lib.mi_moe_gemm(_ptr(x), dt, H, _ptr(gate_up), _ptr(act), _ptr(sorted_pair), _ptr(tile_expert), tiles, tile, ff, H, top, 1, st))
-  _check(lib, lib.mi_moe_gemm(_ptr(act), dt, ff, _ptr(down), _ptr(y), _ptr(sorted_pair), _ptr(tile_expert), tiles, tile, H, ff, top, 0, st))
+  busy = min(tiles, min(E, pairs) + pairs // tile)      # row tiles that can hold rows at all
+  _check(lib, lib.mi_moe_gemm(_ptr(x), dt, H, _ptr(gate_up), _ptr(act), _ptr(sorted_pair), _ptr(tile_expert), tiles, tile, ff, H, top, 1, busy, st))
+  _check(lib, lib.mi_moe_gemm(_ptr(act), dt, ff, _ptr(down), _ptr(y), _ptr(sorted_pair), _ptr(tile_expert), tiles, tile, H, ff, top, 0, busy, st))
   _check(lib, lib.mi_moe_combine(_ptr(out), _dt(out), _ptr(y), F32, _ptr(pos_of), _ptr(wts), T, top, H, st))
 
 

@@ -64,8 +64,8 @@ class SwiGLUFeedForward(FeedForward):
 class RoutedExpertsFeedForward(FeedForward):
   """A mixture of ``num_experts`` small SwiGLU feed-forward layers of which each token uses ``top``.
 
-  Router logits ``z = W_router h`` and scores ``s = sigmoid(z)`` in float32 (the router matrix is kept in float32; ``h``
-  is the normalised row in the compute dtype).  The experts of the ``top`` largest ``s + correction`` are chosen;
+  Router logits ``z = W_router h`` accumulated in float32 by the engine's matrix product (in bfloat16 mode both operands
+  are bfloat16, whose products are exact in float32) and scores ``s = sigmoid(z)`` in float32.  The experts of the ``top`` largest ``s + correction`` are chosen;
   their weights are their ``s`` (without the correction) divided by the sum of those ``s`` (+ 1e-20); the output is
   the weighted sum of the chosen experts' outputs.  The experts' matrices are stacked: ``gate_up [E, 2 ff, H]`` (an
   expert's gate rows, then its up rows), ``down [E, H, ff]``.  File tensors: ``<name>.router``, ``<name>.correction``,
@@ -85,7 +85,7 @@ class RoutedExpertsFeedForward(FeedForward):
     gate_up = [p for e in range(E) for p in (Piece(f"{n}.e{e}.gate", 2 * F * e, (F, H)), Piece(f"{n}.e{e}.up", 2 * F * e + F, (F, H)))]
     down = [Piece(f"{n}.e{e}.down", H * e, (H, F)) for e in range(E)]
     return {
-      "router": ParamSpec((E, H), "matrix_f32", [whole(f"{n}.router", (E, H))], init="fan_in"),
+      "router": ParamSpec((E, H), "matrix", [whole(f"{n}.router", (E, H))], init="fan_in"),
       "correction": ParamSpec((E,), "vector", [whole(f"{n}.correction", (E,))]),
       "gate_up": ParamSpec((2 * F * E, H), "matrix", [gate_up]),
       "down": ParamSpec((H * E, F), "matrix", [down]),

@@ -81,7 +81,7 @@ def test_weights_are_asked_for_by_name(model_p, tmp_path):
   assert torch.equal(mixer.qkvg[mixer.g_off:].float(), W["l1.mix.g"]) and torch.equal(mixer.qkvg[mixer.k_off:mixer.v_off].float(), W["l1.mix.k"])
   assert mixer.mix.shape == () and mixer.sink.dtype == torch.float32
   ffn = spec.blocks[1].ffn
-  assert ffn.router.dtype == torch.float32 and torch.equal(ffn.router, W["l1.mlp.router"])
+  assert torch.equal(ffn.router.float(), W["l1.mlp.router"]) and ffn.correction.dtype == torch.float32
   assert torch.equal(ffn.gate_up.view(5, 80, 64)[3, 40:].float(), W["l1.mlp.e3.up"]) and torch.equal(ffn.down.view(5, 64, 40)[4].float(), W["l1.mlp.e4.down"])
   # a file with a tensor missing, one too many and one of a wrong shape: one error names all three
   t = load_file(f"{model_p}/model.safetensors")

@@ -243,13 +243,13 @@ def test_routed_experts(dtype, T, W, F, E, top):
   out = torch.empty((T, W), dtype=dtype, device=DEV)
   ws = Workspace(torch.device(DEV))
   for _ in range(2):                                     # twice: the scratch of the first call is used again
-    ops.routed_experts(out, h.to(DEV), Wt["router"].to(DEV), Wt["correction"].to(DEV), gate_up, down, top, ws)
+    ops.routed_experts(out, h.to(DEV), Wt["router"].to(dtype).to(DEV), Wt["correction"].to(DEV), gate_up, down, top, ws)
   err = (out.float().cpu() - want).abs().max(-1).values
   assert int(clear.sum()) >= 0.7 * T
   assert float(err[clear].max()) <= (1e-4 if dtype == torch.float32 else 4e-2), f"worst rows: {err.topk(min(5, T))}"
   # the weights of a token add up to one: with every expert the same, the mixture is that expert
   for e in range(1, E):
     gate_up[e], down[e] = gate_up[0], down[0]
-  ops.routed_experts(out, h.to(DEV), Wt["router"].to(DEV), Wt["correction"].to(DEV), gate_up, down, top, ws)
+  ops.routed_experts(out, h.to(DEV), Wt["router"].to(dtype).to(DEV), Wt["correction"].to(DEV), gate_up, down, top, ws)
   one = plain.swiglu(h.float(), Wt["e0.gate"], Wt["e0.up"], Wt["e0.down"])
   assert float((out.float().cpu() - one).abs().max()) <= (1e-4 if dtype == torch.float32 else 4e-2)
