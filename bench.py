@@ -686,7 +686,7 @@ def _compare_groups(times: dict) -> dict:
   for name, us in times.items():
     if re.search(r"decode_tma_kernel|decode_cluster_kernel|decode_split_kernel|decode_merge|attention_prefill|attention_generic", name):
       g["attention"] += us
-    elif "moe_gemm" in name or re.search(r"gemm_tc_kernel<\w+, \w+, (true|\(bool\)1)>", name):     # the grouped instantiation of the tcgen05 product
+    elif "moe_gemm" in name or "moe_stream" in name or re.search(r"gemm_tc_kernel<\w+, \w+, (true|\(bool\)1)>", name):     # the grouped instantiation of the tcgen05 product
       g["experts"] += us
     elif re.search(r"moe_route|moe_align|moe_combine", name):
       g["routing"] += us

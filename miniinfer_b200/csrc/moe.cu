@@ -15,8 +15,8 @@
 //
 // A pair's products depend on its own row and its expert's weights only (sums over k in a fixed order), and a
 // token's sum runs over its choices in order, so a token's output does not depend on the rest of the batch.
-// bfloat16: mma.m16n8k16 with float32 accumulation, tiles through shared memory by cp.async in two
-// stages; float32: plain FMA in the order of k.
+// bfloat16: mma.m16n8k16 with float32 accumulation - row tiles of 64 through shared memory by cp.async (three slices of K
+// in flight), row tiles of 16 with the weights streamed into registers; float32: plain FMA in the order of k.
 #include "common.cuh"
 
 namespace {
@@ -170,14 +170,16 @@ constexpr int GLDS = GBK + 8;    // shared-memory row stride in elements (odd nu
 constexpr int WN_COLS = 32;      // columns of a warp's tile
 
 // WM x WN warps; a warp owns 16 rows x 32 columns (of gate and of up, if SWIGLU).  Block tile: 16 WM rows x 32 WN columns.
-template <int WM, int WN, bool SWIGLU>
+// STAGES slices of 64 elements of K are in flight: with few rows an expert the kernel streams weights, and what a block
+// has asked for is what keeps the memory busy - narrow tiles take more stages.
+template <int WM, int WN, bool SWIGLU, int STAGES>
 __global__ void __launch_bounds__(WM * WN * 32)
 moe_gemm_bf16_kernel(GroupedArgs a) {
   constexpr int TM = 16 * WM, BN = WN_COLS * WN, THREADS = WM * WN * 32;
   constexpr int NB = SWIGLU ? 2 : 1;
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  __nv_bfloat16* as = reinterpret_cast<__nv_bfloat16*>(smem_raw);        // [2][TM][GLDS]
-  __nv_bfloat16* bs = as + 2 * TM * GLDS;                                // [2][NB][BN][GLDS]
+  __nv_bfloat16* as = reinterpret_cast<__nv_bfloat16*>(smem_raw);        // [STAGES][TM][GLDS]
+  __nv_bfloat16* bs = as + STAGES * TM * GLDS;                           // [STAGES][NB][BN][GLDS]
   __shared__ int s_row[TM];
   const int tile = blockIdx.y, n0 = blockIdx.x * BN;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -224,18 +226,20 @@ moe_gemm_bf16_kernel(GroupedArgs a) {
       for (int c = 0; c < 4; ++c) acc[b][i][c] = 0.f;
 
   const int nk = (K + GBK - 1) / GBK;
-  load(0, 0);
-  cp_async_commit();
+#pragma unroll
+  for (int st = 0; st < STAGES - 1; ++st) {
+    if (st < nk) load(st, st * GBK);
+    cp_async_commit();
+  }
   for (int kb = 0; kb < nk; ++kb) {
-    const int stage = kb & 1;
-    if (kb + 1 < nk) {
-      load(stage ^ 1, (kb + 1) * GBK);
+    const int stage = kb % STAGES;
+    cp_async_wait<STAGES - 2>();       // slice kb has landed
+    __syncthreads();                   // ... for every thread; and everyone is done with slice kb - 1, whose stage is asked for next
+    {
+      const int nxt = kb + STAGES - 1;
+      if (nxt < nk) load(nxt % STAGES, nxt * GBK);
       cp_async_commit();
-      cp_async_wait<1>();
-    } else {
-      cp_async_wait<0>();
     }
-    __syncthreads();
     const __nv_bfloat16* at = as + stage * TM * GLDS + (wm * 16 + (lm & 1) * 8 + lr) * GLDS + (lm >> 1) * 8;
 #pragma unroll
     for (int k = 0; k < GBK / 16; ++k) {
@@ -253,8 +257,8 @@ moe_gemm_bf16_kernel(GroupedArgs a) {
         }
       }
     }
-    __syncthreads();
   }
+  cp_async_wait<0>();
 
   // rows g and g + 8 of the warp's 16, columns wn * 32 + i * 8 + 2 t (+1)
 #pragma unroll
@@ -278,6 +282,108 @@ moe_gemm_bf16_kernel(GroupedArgs a) {
         if (n + 1 < N) o[1] = acc[0][i][2 * h + 1];
       }
     }
+  }
+}
+
+// Few rows an expert (a decode step): the time goes into reading each expert's matrices once, so the weights go from
+// global memory straight to the registers of the warp that multiplies them - 16-byte loads that bypass L1, four slices
+// of K asked for before the first is used - as in the engine's few-row product for dense matrices.  A block of eight
+// warps owns a row tile of 16 rows and 8 * (8 / KS) output columns; KS warps share a group of 8 columns (of gate and
+// of up, if SWIGLU) and deal the 32-element slices of K among them, and their partial tiles are added through shared
+// memory in the order of the warps, so a value is a function of (N, K) alone.  The k index inside a slice is permuted
+// the same way for both operands, so that a thread's 16-byte load is its fragment of two consecutive MMAs.
+__device__ __forceinline__ uint4 ld_stream16(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+  return v;
+}
+
+constexpr int SW = 8;       // warps of a block of the streaming product
+
+template <bool SWIGLU, int KS>
+__global__ void __launch_bounds__(SW * 32)
+moe_stream_bf16_kernel(GroupedArgs a) {
+  constexpr int NB = SWIGLU ? 2 : 1, GROUPS = SW / KS, U = 4;
+  __shared__ float red[SW][16][NB * 8 + 1];
+  __shared__ int s_row[16];
+  const int tile = blockIdx.y;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int g = lane >> 2, t = lane & 3;
+  const int group = warp / KS, kpart = warp % KS;
+  const int n0 = (blockIdx.x * GROUPS + group) * 8;
+  mi::grid_dependency_sync();
+  const int e = a.tile_expert[tile];
+  if (e < 0) return;
+  if (threadIdx.x < 16) {
+    const int pair = a.sorted_pair[tile * 16 + threadIdx.x];
+    s_row[threadIdx.x] = pair < 0 ? -1 : (a.gather ? pair / a.top : tile * 16 + (int)threadIdx.x);
+  }
+  __syncthreads();
+  const int K = a.K, N = a.N;
+  const __nv_bfloat16* A = (const __nv_bfloat16*)a.a;
+  const __nv_bfloat16* W = (const __nv_bfloat16*)a.w + (size_t)e * a.w_expert_stride;
+  const int ra = s_row[g], rb = s_row[g + 8];
+  const __nv_bfloat16* xa = ra >= 0 ? A + (size_t)ra * a.a_stride : nullptr;
+  const __nv_bfloat16* xb = rb >= 0 ? A + (size_t)rb * a.a_stride : nullptr;
+  const bool col_ok = n0 + g < N;
+  const __nv_bfloat16* wrow[NB];
+#pragma unroll
+  for (int b = 0; b < NB; ++b) wrow[b] = W + ((size_t)b * N + n0 + g) * K;
+  float acc[NB][4];
+#pragma unroll
+  for (int b = 0; b < NB; ++b)
+#pragma unroll
+    for (int c = 0; c < 4; ++c) acc[b][c] = 0.f;
+  const uint4 zero = make_uint4(0, 0, 0, 0);
+  const int nkb = (K + 31) / 32;
+  for (int kb0 = kpart; kb0 < nkb; kb0 += KS * U) {
+    uint4 wv[U][NB], va[U], vb[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int k = (kb0 + u * KS) * 32 + 8 * t;
+      const bool ok = kb0 + u * KS < nkb && k < K;
+#pragma unroll
+      for (int b = 0; b < NB; ++b) wv[u][b] = (ok && col_ok) ? ld_stream16(wrow[b] + k) : zero;
+      va[u] = (ok && xa) ? __ldg(reinterpret_cast<const uint4*>(xa + k)) : zero;
+      vb[u] = (ok && xb) ? __ldg(reinterpret_cast<const uint4*>(xb + k)) : zero;
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const uint32_t aa[4] = {va[u].x, va[u].y, va[u].z, va[u].w}, ab[4] = {vb[u].x, vb[u].y, vb[u].z, vb[u].w};
+#pragma unroll
+      for (int b = 0; b < NB; ++b) {
+        const uint32_t ww[4] = {wv[u][b].x, wv[u][b].y, wv[u][b].z, wv[u][b].w};
+#pragma unroll
+        for (int m = 0; m < 2; ++m) {
+          const uint32_t af[4] = {aa[2 * m], ab[2 * m], aa[2 * m + 1], ab[2 * m + 1]};
+          mma_bf16(acc[b], af, ww[2 * m], ww[2 * m + 1]);
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int b = 0; b < NB; ++b) {
+    red[warp][g][b * 8 + 2 * t] = acc[b][0];
+    red[warp][g][b * 8 + 2 * t + 1] = acc[b][1];
+    red[warp][g + 8][b * 8 + 2 * t] = acc[b][2];
+    red[warp][g + 8][b * 8 + 2 * t + 1] = acc[b][3];
+  }
+  __syncthreads();
+  // 16 rows x 8 columns per group: a thread each, the KS partial tiles added in the order of the warps
+  for (int idx = threadIdx.x; idx < GROUPS * 128; idx += SW * 32) {
+    const int grp = idx / 128, r = (idx % 128) / 8, c = idx % 8;
+    const int n = (blockIdx.x * GROUPS + grp) * 8 + c;
+    if (s_row[r] < 0 || n >= N) continue;
+    float v[NB];
+#pragma unroll
+    for (int b = 0; b < NB; ++b) {
+      v[b] = 0.f;
+#pragma unroll
+      for (int k = 0; k < KS; ++k) v[b] += red[grp * KS + k][r][b * 8 + c];
+    }
+    const size_t o = (size_t)(tile * 16 + r) * N + n;
+    if (SWIGLU) ((__nv_bfloat16*)a.out)[o] = __float2bfloat16_rn(mi::silu_mul_fast(v[0], v[NB - 1]));
+    else ((float*)a.out)[o] = v[0];
   }
 }
 
@@ -367,17 +473,17 @@ moe_gather_kernel(__nv_bfloat16* __restrict__ xs, const __nv_bfloat16* __restric
   for (int i = threadIdx.x; i < H8; i += blockDim.x) dst[i] = src ? src[i] : make_uint4(0, 0, 0, 0);
 }
 
-template <int WM, int WN, bool SWIGLU>
+template <int WM, int WN, bool SWIGLU, int STAGES>
 int launch_bf16(const GroupedArgs& a, int tiles, cudaStream_t stream) {
   constexpr int TM = 16 * WM, BN = WN_COLS * WN;
-  const size_t smem = (size_t)(2 * TM + 2 * (SWIGLU ? 2 : 1) * BN) * GLDS * sizeof(__nv_bfloat16);
+  const size_t smem = (size_t)STAGES * (TM + (SWIGLU ? 2 : 1) * BN) * GLDS * sizeof(__nv_bfloat16);
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(moe_gemm_bf16_kernel<WM, WN, SWIGLU>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = cudaFuncSetAttribute(moe_gemm_bf16_kernel<WM, WN, SWIGLU, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return mi_fail("moe_gemm: cannot get %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
     configured = true;
   }
-  mi::launch(moe_gemm_bf16_kernel<WM, WN, SWIGLU>, dim3((a.N + BN - 1) / BN, tiles), dim3(WM * WN * 32), smem, stream, a);
+  mi::launch(moe_gemm_bf16_kernel<WM, WN, SWIGLU, STAGES>, dim3((a.N + BN - 1) / BN, tiles), dim3(WM * WN * 32), smem, stream, a);
   return 0;
 }
 
@@ -431,15 +537,22 @@ MI_API int mi_moe_gemm(const void* a_rows, int dtype, int a_stride, const void* 
     MI_REQUIRE(K % 8 == 0 && a_stride % 8 == 0, "moe_gemm: K=%d and the row stride %d must be multiples of 8 in bfloat16", K, a_stride);
     MI_REQUIRE(((uintptr_t)a_rows % 16) == 0 && ((uintptr_t)w % 16) == 0, "moe_gemm: operands must be 16-byte aligned");
     int rc;
-    if (TM == 64) rc = swiglu ? launch_bf16<4, 2, true>(g, max_tiles, stream) : launch_bf16<4, 2, false>(g, max_tiles, stream);
+    if (TM == 64) rc = swiglu ? launch_bf16<4, 2, true, 3>(g, max_tiles, stream) : launch_bf16<4, 2, false, 3>(g, max_tiles, stream);
     else if (TM == 16) {
-      // few rows an expert: the weights are streamed once, so the columns are cut finely enough to put about two blocks
-      // on every SM (`busy_tiles`: the row tiles that can have rows at all)
-      const int sms = mi::sm_count();
-      const int busy = busy_tiles > 0 && busy_tiles < max_tiles ? busy_tiles : max_tiles;
-      if ((long long)((N + 127) / 128) * busy >= 2LL * sms) rc = swiglu ? launch_bf16<1, 4, true>(g, max_tiles, stream) : launch_bf16<1, 4, false>(g, max_tiles, stream);
-      else if ((long long)((N + 63) / 64) * busy >= 2LL * sms) rc = swiglu ? launch_bf16<1, 2, true>(g, max_tiles, stream) : launch_bf16<1, 2, false>(g, max_tiles, stream);
-      else rc = swiglu ? launch_bf16<1, 1, true>(g, max_tiles, stream) : launch_bf16<1, 1, false>(g, max_tiles, stream);
+      // few rows an expert: the weights are streamed once, straight into registers; K is dealt to eight warps where it
+      // is long, to four (two groups of columns a block) where it is short
+      (void)busy_tiles;
+      MI_REQUIRE((N + 7) / 8 <= 65535 * 2, "moe_gemm: too many columns for one launch");
+      rc = 0;
+      if (K >= 1024) {
+        const dim3 grid((N + 7) / 8, max_tiles);
+        if (swiglu) mi::launch(moe_stream_bf16_kernel<true, 8>, grid, dim3(SW * 32), 0, stream, g);
+        else mi::launch(moe_stream_bf16_kernel<false, 8>, grid, dim3(SW * 32), 0, stream, g);
+      } else {
+        const dim3 grid((N + 15) / 16, max_tiles);
+        if (swiglu) mi::launch(moe_stream_bf16_kernel<true, 4>, grid, dim3(SW * 32), 0, stream, g);
+        else mi::launch(moe_stream_bf16_kernel<false, 4>, grid, dim3(SW * 32), 0, stream, g);
+      }
     }
     else return mi_fail("moe_gemm: row tiles of 16 or 64 in bfloat16, got %d", TM);
     if (rc) return rc;
