@@ -472,6 +472,16 @@ def kernel_case(name: str, reps: int = 3) -> str:
     fn, what = attention_case(torch.bfloat16, 16, [(2048, 2048)])           # pages of 16 tokens: not the tcgen05 kernel's
   elif name == "attention_decode_cpasync":
     fn, what = attention_case(torch.bfloat16, 16, [(2048 + 8 * i, 1) for i in range(64)])
+  elif name in ("experts_many_rows", "experts_few_rows"):
+    # a mixture of 32 experts (each 2 x 1536 x 4096 gate-and-up and 4096 x 1536 down: 1.2 GB in all), 8 a token:
+    # 2048 tokens run the tcgen05 grouped product, 8 tokens the kernel that streams the chosen experts' weights
+    T, W, F, E, top = (2048 if name == "experts_many_rows" else 8), 4096, 1536, 32, 8
+    x = rnd(T, W)
+    router, corr = rnd(E, W, scale=1.5 / W ** 0.5), rnd(E, dtype=torch.float32, scale=0.02)
+    gate_up, down = rnd(E, 2 * F, W, scale=0.02), rnd(E, W, F, scale=0.02)
+    out = torch.empty(T, W, dtype=torch.bfloat16, device=dev)
+    fn = lambda: ops.routed_experts(out, x, router, corr, gate_up, down, top, ws)
+    what = f"{T} tokens, {E} experts of 3 x {F} x {W}, {top} a token ({T * top * 3 * 2 * F * W / 1e9:.1f} GFLOP)"
   else:
     raise SystemExit(f"unknown kernel case {name!r}")
   fn()
@@ -486,7 +496,7 @@ def kernel_case(name: str, reps: int = 3) -> str:
 
 
 KERNEL_CASES = ("sample", "silu_mul", "gemm_f32", "gemm_tc_plain", "gemm_stream", "attention_generic", "attention_prefill_tc",
-                "attention_prefill_tc_pairs", "attention_prefill_mma", "attention_decode_cpasync")
+                "attention_prefill_tc_pairs", "attention_prefill_mma", "attention_decode_cpasync", "experts_many_rows", "experts_few_rows")
 
 
 def mixed_workload(model_dir: str, requests: int = 64, outputs: int = 256) -> dict:
