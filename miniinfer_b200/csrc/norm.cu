@@ -177,6 +177,86 @@ __global__ void add_layernorm_kernel(TOut* __restrict__ out, float* __restrict__
     o[h] = mi::from_float<TOut>((ln_row[h] - mean) * rstd * w[h] + b[h]);
 }
 
+
+// Rows whose length is a multiple of 4, up to 8192: 16-byte steps, the row kept in registers between the passes.
+template <typename TD> struct Delta4;
+template <> struct Delta4<__nv_bfloat16> {
+  static __device__ __forceinline__ float4 load(const __nv_bfloat16* p) {
+    const uint2 raw = *reinterpret_cast<const uint2*>(p);
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+    return make_float4(a.x, a.y, b.x, b.y);
+  }
+};
+template <> struct Delta4<float> {
+  static __device__ __forceinline__ float4 load(const float* p) { return *reinterpret_cast<const float4*>(p); }
+};
+__device__ __forceinline__ void store4(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+__device__ __forceinline__ void store4(__nv_bfloat16* p, float4 v) {
+  const __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+  uint2 packed;
+  packed.x = *reinterpret_cast<const uint32_t*>(&lo);
+  packed.y = *reinterpret_cast<const uint32_t*>(&hi);
+  *reinterpret_cast<uint2*>(p) = packed;
+}
+
+template <typename TOut, typename TDelta, int VPT>
+__global__ void __launch_bounds__(256)
+add_layernorm_vec_kernel(TOut* __restrict__ out, float* __restrict__ resid, const TDelta* __restrict__ d1,
+                         const TDelta* __restrict__ d2, const float* __restrict__ w, const float* __restrict__ b,
+                         const int* __restrict__ rows, int H, float eps, int write_back) {
+  __shared__ float scratch[33];
+  const int r = blockIdx.x;
+  const int H4 = H / 4;
+  const int row = rows ? rows[r] : r;       // the row list, weights and biases are written by no kernel
+  float4 ww[VPT], bb[VPT];
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int h = threadIdx.x + i * 256;
+    if (h < H4) { ww[i] = reinterpret_cast<const float4*>(w)[h]; bb[i] = reinterpret_cast<const float4*>(b)[h]; }
+  }
+  mi::grid_dependency_sync();
+  float* x = resid + (size_t)row * H;
+  const TDelta* a = d1 ? d1 + (size_t)row * H : nullptr;
+  const TDelta* c = d2 ? d2 + (size_t)row * H : nullptr;
+  float4 v[VPT];
+  float s = 0.f;
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int h = threadIdx.x + i * 256;
+    if (h < H4) {
+      v[i] = reinterpret_cast<const float4*>(x)[h];
+      if (a || c) {
+        float4 add = a ? Delta4<TDelta>::load(a + 4 * h) : make_float4(0.f, 0.f, 0.f, 0.f);
+        if (a && c) { const float4 t = Delta4<TDelta>::load(c + 4 * h); add.x += t.x; add.y += t.y; add.z += t.z; add.w += t.w; }
+        else if (c) add = Delta4<TDelta>::load(c + 4 * h);
+        v[i].x += add.x; v[i].y += add.y; v[i].z += add.z; v[i].w += add.w;
+        if (write_back) reinterpret_cast<float4*>(x)[h] = v[i];
+      }
+      s += (v[i].x + v[i].y) + (v[i].z + v[i].w);
+    }
+  }
+  const float mean = mi::block_sum(s, scratch) / (float)H;
+  float q = 0.f;
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int h = threadIdx.x + i * 256;
+    if (h < H4) {
+      const float dx = v[i].x - mean, dy = v[i].y - mean, dz = v[i].z - mean, dw = v[i].w - mean;
+      q += (dx * dx + dy * dy) + (dz * dz + dw * dw);
+    }
+  }
+  const float rstd = 1.f / sqrtf(mi::block_sum(q, scratch) / (float)H + eps);
+  TOut* o = out + (size_t)r * H;
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int h = threadIdx.x + i * 256;
+    if (h < H4)
+      store4(o + 4 * h, make_float4((v[i].x - mean) * rstd * ww[i].x + bb[i].x, (v[i].y - mean) * rstd * ww[i].y + bb[i].y,
+                                    (v[i].z - mean) * rstd * ww[i].z + bb[i].z, (v[i].w - mean) * rstd * ww[i].w + bb[i].w));
+  }
+}
+
 }  // namespace
 
 MI_API int mi_add_layernorm(void* out, int out_dtype, float* resid, const void* d1, const void* d2, int delta_dtype,
@@ -187,14 +267,26 @@ MI_API int mi_add_layernorm(void* out, int out_dtype, float* resid, const void* 
   if (R == 0) return 0;
   const int threads = 256;  // fixed: the order of the reductions must not depend on the batch
   const size_t smem = (size_t)H * sizeof(float);
-#define MI_LN_LAUNCH(TO, TD) \
-  mi::launch(add_layernorm_kernel<TO, TD>, dim3(R), dim3(threads), smem, stream, (TO*)out, resid, (const TD*)d1, (const TD*)d2, w, b, rows, H, eps, write_back)
+  const bool vec = H % 4 == 0 && H <= 8192 && ((uintptr_t)out % 16) == 0 && ((uintptr_t)resid % 16) == 0 && ((uintptr_t)d1 % 16) == 0 &&
+                   ((uintptr_t)d2 % 16) == 0 && ((uintptr_t)w % 16) == 0 && ((uintptr_t)b % 16) == 0;
+  const int vpt = (H / 4 + 255) / 256;
+#define MI_LN_VEC(TO, TD, V) \
+  mi::launch(add_layernorm_vec_kernel<TO, TD, V>, dim3(R), dim3(threads), 0, stream, (TO*)out, resid, (const TD*)d1, (const TD*)d2, w, b, rows, H, eps, write_back)
+#define MI_LN_LAUNCH(TO, TD)                                      \
+  do {                                                            \
+    if (vec && vpt <= 1) MI_LN_VEC(TO, TD, 1);                    \
+    else if (vec && vpt <= 2) MI_LN_VEC(TO, TD, 2);               \
+    else if (vec && vpt <= 4) MI_LN_VEC(TO, TD, 4);               \
+    else if (vec) MI_LN_VEC(TO, TD, 8);                           \
+    else mi::launch(add_layernorm_kernel<TO, TD>, dim3(R), dim3(threads), smem, stream, (TO*)out, resid, (const TD*)d1, (const TD*)d2, w, b, rows, H, eps, write_back); \
+  } while (0)
   if (out_dtype == MI_BF16 && delta_dtype == MI_BF16) MI_LN_LAUNCH(__nv_bfloat16, __nv_bfloat16);
   else if (out_dtype == MI_F32 && delta_dtype == MI_F32) MI_LN_LAUNCH(float, float);
   else if (out_dtype == MI_BF16 && delta_dtype == MI_F32) MI_LN_LAUNCH(__nv_bfloat16, float);
   else if (out_dtype == MI_F32 && delta_dtype == MI_BF16) MI_LN_LAUNCH(float, __nv_bfloat16);
   else return mi_fail("layernorm: unknown dtypes out=%d delta=%d", out_dtype, delta_dtype);
 #undef MI_LN_LAUNCH
+#undef MI_LN_VEC
   MI_LAUNCH_OK("add_layernorm");
   return 0;
 }

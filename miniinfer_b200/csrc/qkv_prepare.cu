@@ -102,6 +102,86 @@ qkv_prepare_kernel(PrepArgs<T> a) {
   }
 }
 
+
+// The same with two values a lane and load (4 bytes of bfloat16, 8 of float32), for the usual case that every size and
+// offset is even: a warp's load covers whole 128-byte lines.
+template <typename T> struct Pair;
+template <> struct Pair<__nv_bfloat16> {
+  static __device__ __forceinline__ float2 load(const __nv_bfloat16* p) { return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(p)); }
+  static __device__ __forceinline__ void store(__nv_bfloat16* p, float a, float b) { *reinterpret_cast<__nv_bfloat162*>(p) = __floats2bfloat162_rn(a, b); }
+};
+template <> struct Pair<float> {
+  static __device__ __forceinline__ float2 load(const float* p) { return *reinterpret_cast<const float2*>(p); }
+  static __device__ __forceinline__ void store(float* p, float a, float b) { *reinterpret_cast<float2*>(p) = make_float2(a, b); }
+};
+
+template <typename T>
+__global__ void __launch_bounds__(PREP_WARPS * 32)
+qkv_prepare_pairs_kernel(PrepArgs<T> a) {
+  constexpr int NP = PREP_MAX_PER_LANE / 2;     // pairs a lane
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int tkn = blockIdx.x;
+  const float lam = (a.v_mode == 2) ? *a.lambda : 0.f;
+  const int slot = a.slot_mapping ? a.slot_mapping[tkn] : -1;
+  mi::grid_dependency_sync();
+  const T* row = a.proj + (size_t)tkn * a.proj_stride;
+  const int units = a.nh + 2 * a.nkv;
+  const int page = slot >= 0 ? slot / a.page_size : 0, off = slot >= 0 ? slot % a.page_size : 0;
+  for (int u = blockIdx.y * PREP_WARPS + warp; u < units; u += PREP_WARPS * gridDim.y) {
+    if (u < a.nh + a.nkv) {
+      const bool is_q = u < a.nh;
+      const int h = is_q ? u : u - a.nh;
+      const T* src = row + (is_q ? a.q_off : a.k_off) + (size_t)h * a.dim;
+      const float* w = is_q ? a.q_w : a.k_w;
+      float2 v[NP];
+      float ss = 0.f;
+#pragma unroll
+      for (int i = 0; i < NP; ++i) {
+        const int d = 2 * lane + 64 * i;
+        v[i] = d < a.dim ? Pair<T>::load(src + d) : make_float2(0.f, 0.f);
+        ss += v[i].x * v[i].x + v[i].y * v[i].y;
+      }
+      float r = 1.f;
+      if (a.normalise) r = 1.f / sqrtf(mi::warp_sum(ss) / (float)a.dim + a.eps);
+      T* dst = nullptr;
+      if (is_q) dst = a.q_out + ((size_t)tkn * a.nh + h) * a.hdp;
+      else if (slot >= 0) dst = a.kv_layer + ((((size_t)page * 2 + 0) * a.nkv + h) * a.page_size + off) * a.hdp;
+      if (dst) {
+#pragma unroll
+        for (int i = 0; i < NP; ++i) {
+          const int d = 2 * lane + 64 * i;
+          if (d < a.hdp) {
+            float y0 = v[i].x * r, y1 = v[i].y * r;
+            if (w && d < a.dim) { y0 *= w[d]; y1 *= w[d + 1]; }
+            Pair<T>::store(dst + d, d < a.dim ? y0 : 0.f, d < a.dim ? y1 : 0.f);
+          }
+        }
+      }
+    } else {
+      const int h = u - a.nh - a.nkv;
+      const T* src = row + a.v_off + (size_t)h * a.vdim;
+      T* other = a.v_other ? a.v_other + ((size_t)tkn * a.nkv + h) * a.vdim : nullptr;
+      T* dst = slot >= 0 ? a.kv_layer + ((((size_t)page * 2 + 1) * a.nkv + h) * a.page_size + off) * a.hdp : nullptr;
+#pragma unroll
+      for (int i = 0; i < NP; ++i) {
+        const int d = 2 * lane + 64 * i;
+        if (d >= a.hdp) continue;
+        float2 y = make_float2(0.f, 0.f);
+        if (d < a.vdim) {
+          y = Pair<T>::load(src + d);
+          if (a.v_mode == 1) Pair<T>::store(other + d, y.x, y.y);
+          else if (a.v_mode == 2) {
+            const float2 o = Pair<T>::load(other + d);
+            y.x = (1.f - lam) * y.x + lam * o.x;
+            y.y = (1.f - lam) * y.y + lam * o.y;
+          }
+        }
+        if (dst) Pair<T>::store(dst + d, y.x, y.y);
+      }
+    }
+  }
+}
+
 }  // namespace
 
 MI_API int mi_qkv_norm_mix_store(const void* proj, int dtype, int proj_stride, int q_off, int k_off, int v_off, int T, int nh,
@@ -115,6 +195,10 @@ MI_API int mi_qkv_norm_mix_store(const void* proj, int dtype, int proj_stride, i
              "qkv_prepare: value mixing needs the other layer's values and lambda");
   MI_REQUIRE(slot_mapping == nullptr || (kv_layer != nullptr && page_size > 0), "qkv_prepare: a store needs the cache layer");
   if (T == 0) return 0;
+  const size_t es = dtype == MI_BF16 ? 2 : 4;
+  const bool pairs = dim % 2 == 0 && vdim % 2 == 0 && hdp % 2 == 0 && proj_stride % 2 == 0 && q_off % 2 == 0 && k_off % 2 == 0 && v_off % 2 == 0 &&
+                     ((uintptr_t)proj % (2 * es)) == 0 && ((uintptr_t)q_out % (2 * es)) == 0 && ((uintptr_t)kv_layer % (2 * es)) == 0 &&
+                     ((uintptr_t)v_other % (2 * es)) == 0;
 #define MI_PREP(TT)                                                                                          \
   do {                                                                                                       \
     PrepArgs<TT> a;                                                                                          \
@@ -122,7 +206,8 @@ MI_API int mi_qkv_norm_mix_store(const void* proj, int dtype, int proj_stride, i
     a.nh = nh; a.nkv = nkv; a.dim = dim; a.vdim = vdim; a.hdp = hdp; a.q_out = (TT*)q_out; a.q_w = q_w; a.k_w = k_w; \
     a.eps = eps; a.normalise = normalise; a.lambda = lambda; a.v_other = (TT*)v_other; a.v_mode = v_mode;     \
     a.slot_mapping = slot_mapping; a.kv_layer = (TT*)kv_layer; a.page_size = page_size;                      \
-    mi::launch(qkv_prepare_kernel<TT>, dim3(T, (nh + 2 * nkv + PREP_WARPS - 1) / PREP_WARPS), dim3(PREP_WARPS * 32), 0, stream, a);                        \
+    if (pairs) mi::launch(qkv_prepare_pairs_kernel<TT>, dim3(T, (nh + 2 * nkv + PREP_WARPS - 1) / PREP_WARPS), dim3(PREP_WARPS * 32), 0, stream, a); \
+    else mi::launch(qkv_prepare_kernel<TT>, dim3(T, (nh + 2 * nkv + PREP_WARPS - 1) / PREP_WARPS), dim3(PREP_WARPS * 32), 0, stream, a);                        \
   } while (0)
   if (dtype == MI_BF16) MI_PREP(__nv_bfloat16);
   else if (dtype == MI_F32) MI_PREP(float);
