@@ -814,12 +814,17 @@ def compare_designs(args) -> int:
             "vocab": COMPARE_VOCAB, "prefill_tokens": PREFILL_TOKENS, "steps": args.steps, "warmup": warmup, "dtype": "bf16",
             "data": "synthetic: random weights, uniform random token ids", "peaks": pk["source"], "sizes": {}}
   kernels_child = args.impl == "compare-child"
+  clocks = None if kernels_child else ClockSampler()
+  if clocks:
+    clocks.start()
   for tag in sizes:
     size = COMPARE_SIZES[tag]
     row = {"size": size}
     for name, cfg in compare_configs(size).items():
       row[name] = compare_one(name, cfg, size, args.batch, args.steps, warmup, pk, kernels_child)
     result["sizes"][tag] = row
+  if clocks:
+    result["clocks"] = clocks.stop()
   if not kernels_child and not args.skip_kernels:
     cmd = [sys.executable, os.path.abspath(__file__), "--impl", "compare-child", "--compare", "rikanex", "--sizes", args.sizes,
            "--batch", str(args.batch), "--context", str(CONTEXT), "--steps", str(args.steps), "--warmup", str(warmup)]

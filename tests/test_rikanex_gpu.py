@@ -166,3 +166,33 @@ def test_greedy_generation_through_the_engine(rikanex_dirs, dtype):
   if DEV != "cpu":
     eng.runner.check_status()
     assert eng.runner.num_graphs() > 0
+
+
+@pytest.mark.skipif(DEV == "cpu", reason="the command line runs on a CUDA device")
+def test_command_line_and_trace_program(rikanex_dirs, tmp_path):
+  """`main.py` generates from a Rikanex folder, and `bin/trace_run` - a process of its own that picks the model by its
+  configuration - replays a mixed trace in both dtypes."""
+  import json
+  import os
+  import subprocess
+  import sys
+  root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+  d = rikanex_dirs("Q")
+  W, cfg = plain.read_weights(d), plain.read_config(d)
+  proc = subprocess.run([sys.executable, os.path.join(root, "main.py"), "--model", d, "--prompt-ids", "5,17,3,200", "--max-tokens", "6",
+                         "--temperature", "0", "--dtype", "float32", "--max-model-len", "64", "--page-size", "16"],
+                        capture_output=True, text=True, timeout=900)
+  assert proc.returncode == 0, proc.stderr[-3000:]
+  assert str(plain.generate(W, cfg, [5, 17, 3, 200], 6)) in proc.stdout
+  reqs = rc.make_requests(cfg["vocab"], (70, 9, 130), seed=2)
+  ref = reference(d, reqs)
+  trace = rc.mixed(reqs, 256, seed=3)
+  for dtype in ("float32", "bfloat16"):
+    out = tmp_path / dtype
+    proc = subprocess.run([os.path.join(root, "bin", "trace_run"), "--model", d, "--dtype", dtype, "--out", str(out), "--max-tokens", "256"],
+                          input="\n".join(json.dumps(r) for r in trace) + "\n", capture_output=True, text=True, timeout=900)
+    assert proc.returncode == 0, proc.stderr[-3000:]
+    assert [l for l in proc.stdout.split("\n") if l.startswith("done")] == [f"done {r['step']}" for r in trace]
+    outputs = {r["step"]: np.fromfile(out / f"{r['step']}.f32", dtype="<f4").reshape(-1, cfg["vocab"])
+               for r in trace if sum(len(e["want"]) for e in r["entries"])}
+    compare(rc.collect(trace, outputs), ref, dtype, "Q", f"trace program {dtype}")
