@@ -521,7 +521,7 @@ MI_API int mi_moe_align(const int* topk_idx, int n_pairs, int E, int TM, int* so
 // swiglu 1: out[row, :N] = silu(a w_gate^T) * (a w_up^T), the expert's matrix holding N gate rows and then N up rows,
 // rows gathered from the tokens; swiglu 0: out[row, :N] = a w^T in float32, rows by position.
 MI_API int mi_moe_gemm(const void* a_rows, int dtype, int a_stride, const void* w, void* out, const int* sorted_pair,
-                       const int* tile_expert, int max_tiles, int TM, int N, int K, int top, int swiglu, int busy_tiles, cudaStream_t stream) {
+                       const int* tile_expert, int max_tiles, int TM, int N, int K, int top, int swiglu, cudaStream_t stream) {
   MI_REQUIRE(N > 0 && K > 0 && max_tiles >= 0 && max_tiles <= 65535, "moe_gemm: bad sizes N=%d K=%d tiles=%d", N, K, max_tiles);
   if (max_tiles == 0) return 0;
   GroupedArgs g;
@@ -541,7 +541,6 @@ MI_API int mi_moe_gemm(const void* a_rows, int dtype, int a_stride, const void* 
     else if (TM == 16) {
       // few rows an expert: the weights are streamed once, straight into registers; K is dealt to eight warps where it
       // is long, to four (two groups of columns a block) where it is short
-      (void)busy_tiles;
       MI_REQUIRE((N + 7) / 8 <= 65535 * 2, "moe_gemm: too many columns for one launch");
       rc = 0;
       if (K >= 1024) {

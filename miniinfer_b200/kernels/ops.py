@@ -481,9 +481,8 @@ def routed_experts(out: torch.Tensor, x: torch.Tensor, router: torch.Tensor, cor
                                             _ptr(status, torch.int32), _tc_pairs(), st))
     _check(lib, lib.mi_moe_combine(_ptr(out), _dt(out), _ptr(y16), BF16, _ptr(pos_of), _ptr(wts), T, top, H, st))
     return
-  busy = min(tiles, min(E, pairs) + pairs // tile)      # row tiles that can hold rows at all
-  _check(lib, lib.mi_moe_gemm(_ptr(x), dt, H, _ptr(gate_up), _ptr(act), _ptr(sorted_pair), _ptr(tile_expert), tiles, tile, ff, H, top, 1, busy, st))
-  _check(lib, lib.mi_moe_gemm(_ptr(act), dt, ff, _ptr(down), _ptr(y), _ptr(sorted_pair), _ptr(tile_expert), tiles, tile, H, ff, top, 0, busy, st))
+  _check(lib, lib.mi_moe_gemm(_ptr(x), dt, H, _ptr(gate_up), _ptr(act), _ptr(sorted_pair), _ptr(tile_expert), tiles, tile, ff, H, top, 1, st))
+  _check(lib, lib.mi_moe_gemm(_ptr(act), dt, ff, _ptr(down), _ptr(y), _ptr(sorted_pair), _ptr(tile_expert), tiles, tile, H, ff, top, 0, st))
   _check(lib, lib.mi_moe_combine(_ptr(out), _dt(out), _ptr(y), F32, _ptr(pos_of), _ptr(wts), T, top, H, st))
 
 

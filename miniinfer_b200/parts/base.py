@@ -47,8 +47,7 @@ class Piece:
 @dataclass
 class ParamSpec:
   """A parameter: its shape, its role (``matrix``/``table``: kept in the compute dtype; ``vector``:
-  kept in float32, scalars included; ``matrix_f32``: a matrix kept in float32 whatever the compute dtype, for what is
-  computed in 32-bit such as a router; ``int``: kept as int32) and the alternative sets of file tensors that fill it."""
+  kept in float32, scalars included; ``int``: kept as int32) and the alternative sets of file tensors that fill it."""
 
   shape: Tuple[int, ...]
   role: str
@@ -56,7 +55,7 @@ class ParamSpec:
   init: str = "normal"            # random-weights mode: "normal" (std given by the model), "ones_noise" (about 1), "half_noise" (about 0.5) or "fan_in" (1.5 / sqrt(columns))
 
   def __post_init__(self):
-    if self.role not in ("matrix", "table", "vector", "matrix_f32", "int"):
+    if self.role not in ("matrix", "table", "vector", "int"):
       raise ValueError(f"unknown parameter role {self.role!r}")
 
 

@@ -22,13 +22,13 @@ and the kernels write only the first ``vdim`` values of an output head.
 
 from __future__ import annotations
 
-from typing import Dict, List, Optional
+from typing import Dict, Optional
 
 import torch
 
 from ..cache.specs import CacheSpec, PagedKVSpec
 from ..kernels import ops
-from .base import ParamSpec, Piece, StepWork, whole
+from .base import ParamSpec, Piece, whole
 from .mixer import AttentionMixer
 
 
@@ -85,9 +85,6 @@ class GatedAttentionMixer(AttentionMixer):
                       ("the fused projection's rows", self.proj_width)):
         if k % 8:
           raise ValueError(f"{self.name}: {what}={k} must be a multiple of 8 in bfloat16 (rows are read 16 bytes at a time)")
-
-  def step_work(self) -> List[StepWork]:
-    return super().step_work()
 
   def takes_residual(self, norm, ctx) -> bool:
     return False

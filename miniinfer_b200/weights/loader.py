@@ -44,7 +44,7 @@ class WeightLoadError(RuntimeError):
 def role_dtype(role: str, compute_dtype: torch.dtype) -> torch.dtype:
   if role in ("matrix", "table"):
     return compute_dtype
-  if role in ("vector", "matrix_f32"):
+  if role == "vector":
     return torch.float32
   return torch.int32
 
