@@ -25,7 +25,7 @@ import torch
 
 STAGING_SLOTS = 8     # pinned snapshots of a block table that uploads in flight may still read
 
-from .specs import CacheSpec, FixedStateSpec, PagedKVSpec
+from .specs import CacheSpec, CompositeSpec, FixedStateSpec, PagedKVSpec, flatten_specs
 
 
 class OutOfPages(RuntimeError):
@@ -86,6 +86,7 @@ class PagedGroup:
     self.page_size = page_size
     self.num_pages = num_pages
     self.max_pages_per_seq = -(-max_model_len // page_size)
+    self.kept_pages = -(-spec.keep_first // page_size) if spec.window is not None else 0   # never given back by the window
     self.allocator = PageAllocator(num_pages)
     self.kv = torch.zeros((num_layers, num_pages + 1, 2, spec.num_kv_heads, page_size, spec.head_dim),
                           dtype=dtype, device=device)
@@ -149,11 +150,12 @@ class StateGroup:
 class LayerCache:
   """What a mixer gets for one entry of the run list."""
 
-  kind: str                       # "paged", "state" or "none"
+  kind: str                       # "paged", "state", "composite" or "none"
   group: int = -1                 # index among the groups of its kind
   tensor: Optional[torch.Tensor] = None   # paged: [page, 2, kv head, token, head_dim]; state: [slot, *shape]
   writes: bool = True             # False: the entry reads the cache another entry writes
   page_size: int = 0
+  members: Optional[List["LayerCache"]] = None   # composite: the caches of the mixer's members, in their order
 
 
 @dataclass
@@ -189,11 +191,15 @@ class KVCacheManager:
     self.paged_groups: List[PagedGroup] = []
     self.state_groups: List[StateGroup] = []
     self._layer_place: List[Optional[tuple]] = []      # (kind, group index, layer index in group)
-    by_spec: Dict[CacheSpec, List[int]] = {}
+    # a place is (layer, member): member -1 for a layer with one need, 0.. for the members of a composite one
+    by_spec: Dict[CacheSpec, List[tuple]] = {}
     for i, spec in enumerate(layer_specs):
-      if spec is not None:
-        by_spec.setdefault(spec, []).append(i)
-    place: Dict[int, tuple] = {}
+      if isinstance(spec, CompositeSpec):
+        for k, member in enumerate(spec.members):
+          by_spec.setdefault(member, []).append((i, k))
+      elif spec is not None:
+        by_spec.setdefault(spec, []).append((i, -1))
+    place: Dict[tuple, tuple] = {}
     for spec, layers in by_spec.items():
       if isinstance(spec, PagedKVSpec):
         g = PagedGroup(len(self.paged_groups), spec, len(layers), page_size,
@@ -209,7 +215,12 @@ class KVCacheManager:
           place[layer] = ("state", s.index, j)
       else:
         raise TypeError(f"unknown cache spec {spec!r}")
-    self._layer_place = [place.get(i) for i in range(len(layer_specs))]
+    self._layer_place = []
+    for i, spec in enumerate(layer_specs):
+      if isinstance(spec, CompositeSpec):
+        self._layer_place.append(("composite", [place[(i, k)] for k in range(len(spec.members))]))
+      else:
+        self._layer_place.append(place.get((i, -1)))
     self._free_slots: List[int] = list(range(max_num_seqs - 1, -1, -1))
     self._requests: Dict[Hashable, _Request] = {}
     self.pad_slot = max_num_seqs
@@ -221,7 +232,7 @@ class KVCacheManager:
     """Pages of the group of ``spec`` when a group that keeps every key has ``num_pages``."""
     if spec.window is None or max_step_tokens is None:
       return num_pages
-    return min(num_pages, max_num_seqs * pages_in_flight(spec.window, page_size, max_step_tokens))
+    return min(num_pages, max_num_seqs * (pages_in_flight(spec.window, page_size, max_step_tokens) + -(-spec.keep_first // page_size)))
 
   @staticmethod
   def bytes_per_page(layer_specs: Sequence[Optional[CacheSpec]], page_size: int, dtype: torch.dtype,
@@ -230,9 +241,21 @@ class KVCacheManager:
     (True) or in those that keep every key (False)."""
     size = torch.empty((), dtype=dtype).element_size()
     total = 0
-    for spec in layer_specs:
+    for spec in flatten_specs(layer_specs):
       if isinstance(spec, PagedKVSpec) and (windowed is None or windowed == (spec.window is not None)):
         total += 2 * spec.num_kv_heads * spec.head_dim * page_size * size
+    return total
+
+  @staticmethod
+  def state_bytes(layer_specs: Sequence[Optional[CacheSpec]], max_num_seqs: int) -> int:
+    """Bytes of the per-request state of all layers, for ``max_num_seqs`` requests and the padding slot."""
+    total = 0
+    for spec in flatten_specs(layer_specs):
+      if isinstance(spec, FixedStateSpec):
+        n = 1
+        for d in spec.shape:
+          n *= int(d)
+        total += n * torch.empty((), dtype=getattr(torch, spec.dtype)).element_size() * (max_num_seqs + 1)
     return total
 
   # ------------------------------------------------------------------ views for the model
@@ -240,7 +263,12 @@ class KVCacheManager:
   def layer_cache(self, cache_layer: Optional[int], writes: bool = True) -> LayerCache:
     if cache_layer is None or self._layer_place[cache_layer] is None:
       return LayerCache(kind="none", writes=False)
-    kind, g, j = self._layer_place[cache_layer]
+    return self._cache_at(self._layer_place[cache_layer], writes)
+
+  def _cache_at(self, where: tuple, writes: bool) -> LayerCache:
+    if where[0] == "composite":
+      return LayerCache("composite", writes=writes, members=[self._cache_at(w, writes) for w in where[1]])
+    kind, g, j = where
     if kind == "paged":
       return LayerCache("paged", g, self.paged_groups[g].kv[j], writes, self.page_size)
     return LayerCache("state", g, self.state_groups[g].state[j], writes, 0)
@@ -324,7 +352,7 @@ class KVCacheManager:
       if g.spec.window is None:
         continue
       first = min(g.first_needed_page(r.length), len(r.pages[g.index]))
-      dead = [i for i in range(first) if r.pages[g.index][i] != 0]
+      dead = [i for i in range(g.kept_pages, first) if r.pages[g.index][i] != 0]
       if dead:
         g.allocator.free([r.pages[g.index][i] for i in dead])
         for i in dead:

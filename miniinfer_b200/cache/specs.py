@@ -13,17 +13,21 @@ from typing import Optional, Tuple, Union
 
 @dataclass(frozen=True)
 class PagedKVSpec:
-  """Keys and values of every position (``window is None``) or of the last ``window`` positions."""
+  """Keys and values of every position (``window is None``) or of the last ``window`` positions; with
+  ``keep_first`` the first positions of a request stay as well, whatever the window has passed."""
 
   num_kv_heads: int
   head_dim: int
   window: Optional[int] = None
+  keep_first: int = 0
 
   def __post_init__(self):
     if self.num_kv_heads <= 0 or self.head_dim <= 0:
       raise ValueError("num_kv_heads and head_dim must be positive")
     if self.window is not None and self.window <= 0:
       raise ValueError("window must be positive or None")
+    if self.keep_first < 0:
+      raise ValueError("keep_first must not be negative")
 
 
 @dataclass(frozen=True)
@@ -38,4 +42,28 @@ class FixedStateSpec:
       raise ValueError("state shape must be positive")
 
 
-CacheSpec = Union[PagedKVSpec, FixedStateSpec]
+@dataclass(frozen=True)
+class CompositeSpec:
+  """What a mixer made of several mixers keeps: the needs of its members, in their order.  The layer's cache is then
+  handed over as one ``LayerCache`` per member (``LayerCache.members``)."""
+
+  members: Tuple[Union[PagedKVSpec, FixedStateSpec], ...]
+
+  def __post_init__(self):
+    if not self.members:
+      raise ValueError("a composite cache need has at least one member")
+
+
+CacheSpec = Union[PagedKVSpec, FixedStateSpec, CompositeSpec]
+
+
+
+def flatten_specs(layer_specs):
+  """The needs of all layers, the members of composite ones one by one, without the layers that keep nothing."""
+  out = []
+  for spec in layer_specs:
+    if isinstance(spec, CompositeSpec):
+      out.extend(spec.members)
+    elif spec is not None:
+      out.append(spec)
+  return out

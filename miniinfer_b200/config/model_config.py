@@ -67,6 +67,10 @@ class ModelConfig:
   def validate(self) -> None:  # pragma: no cover - overridden
     pass
 
+  def read_tensor_shapes(self, shapes: Dict[str, tuple]) -> None:
+    """For designs in which a size is given by a tensor's shape alone: called with the shapes of the weights file's tensors
+    when a configuration is read from a model folder.  Default: nothing to learn."""
+
 
 @dataclass
 class Qwen3Config(ModelConfig):
@@ -259,5 +263,235 @@ class RikanexConfig(ModelConfig):
   def to_dict(self) -> Dict[str, Any]:
     d = {"architecture": self.architecture, "vocab": self.vocab, "width": self.width, "embedding": dict(self.embedding),
          "norm": dict(self.norm), "layers": [dict(x) for x in self.layers]}
+    d.update(self.extra)
+    return d
+
+
+def _positive_int(d: dict, key: str, where: str) -> int:
+  v = d.get(key)
+  if not isinstance(v, int) or isinstance(v, bool) or v <= 0:
+    raise ConfigError(f"{where}.{key} must be a positive integer, got {v!r}")
+  return v
+
+
+def _number(d: dict, key: str, where: str, positive: bool = True) -> float:
+  v = d.get(key)
+  if not isinstance(v, (int, float)) or isinstance(v, bool) or (positive and not v > 0):
+    raise ConfigError(f"{where}.{key} must be a {'positive ' if positive else ''}number, got {v!r}")
+  return float(v)
+
+
+@dataclass
+class RotationConfig:
+  """``rot``: ``dims`` rotated values of a head, ``base`` of the frequencies, and optionally ``scaling`` {factor, original,
+  fast, slow} (frequencies stretched for contexts beyond ``original``)."""
+
+  dims: int
+  base: float
+  scaling: Optional[Dict[str, float]] = None
+
+  @classmethod
+  def read(cls, m: dict, where: str) -> "RotationConfig":
+    rot = m.get("rot")
+    if not isinstance(rot, dict):
+      raise ConfigError(f"{where}.rot is missing")
+    dims = _positive_int(rot, "dims", f"{where}.rot")
+    if dims % 2:
+      raise ConfigError(f"{where}.rot.dims must be even, got {dims}")
+    base = _number(rot, "base", f"{where}.rot")
+    scaling = rot.get("scaling")
+    if scaling is not None:
+      if not isinstance(scaling, dict):
+        raise ConfigError(f"{where}.rot.scaling must be an object")
+      scaling = {k: _number(scaling, k, f"{where}.rot.scaling") for k in ("factor", "original", "fast", "slow")}
+    return cls(dims, base, scaling)
+
+
+@dataclass
+class LatentAttentionConfig:
+  """``layers[i].mixer`` of a ``latent_attention`` layer."""
+
+  heads: int
+  dim: int            # unrotated query/key values a head
+  rot_dim: int        # rotated ones
+  vdim: int
+  q_rank: int
+  kv_rank: int
+  scale: float
+  rot: RotationConfig
+
+
+@dataclass
+class WindowedAttentionConfig:
+  """The left member of a ``parallel`` layer's mixer: grouped-query attention whose values are its keys."""
+
+  heads: int
+  kv_heads: int
+  dim: int
+  vdim: int
+  scale: float
+  window: Optional[int]      # ``mask.size``
+  keep_first: int            # ``mask.keep_first``
+  rot: RotationConfig
+
+
+@dataclass
+class GatedDeltaConfig:
+  """The right member of a ``parallel`` layer's mixer.  The two low ranks are read from the tensors' shapes."""
+
+  heads: int
+  kv_heads: int
+  dim: int
+  vdim: int
+  conv: int
+
+
+@dataclass
+class SelectiveScanConfig:
+  """``layers[i].mixer`` of a ``mamba1`` layer."""
+
+  inner: int
+  state: int
+  dt_rank: int
+  conv: int
+
+
+@dataclass
+class VugudraConfig(ModelConfig):
+  """Vugudra: a decoder whose layers are listed one by one (``layers[i].{type, mixer, mlp}``), each a block of a mixer and
+  a dense feed-forward side by side with a norm of its own each; mixers of three types - ``latent_attention``, ``parallel``
+  (windowed attention beside a gated delta rule) and ``mamba1`` (selective scan); ``loop`` {start, stop, times} runs the layers
+  start .. stop - 1 ``times`` times in a row with the same weights.  Other keys: ``architecture``, ``vocab``, ``width``,
+  ``norm.eps``.  ``low_ranks`` is not a key of the file: where a size is given by a tensor's shape only (the two low ranks of
+  the delta rule's decay and gate), the loader of the configuration reads it from the weights file's header.  The design
+  has no position limit of its own; ``max_position_embeddings`` is only the engine's bound."""
+
+  architecture: str = "Vugudra"
+  vocab: int = 0
+  width: int = 0
+  norm: Dict[str, Any] = field(default_factory=dict)
+  layers: List[Dict[str, Any]] = field(default_factory=list)
+  loop: Optional[Dict[str, Any]] = None
+  max_position_embeddings: int = 1 << 30
+  initializer_range: float = 0.02
+  low_ranks: Optional[Dict[str, int]] = None      # "<layer>.decay" / "<layer>.gate" -> rank, when known
+
+  TYPES = ("latent_attention", "parallel", "mamba1")
+
+  def validate(self) -> None:
+    if not self.architectures:
+      self.architectures = [self.architecture]
+    self.vocab_size = self.vocab
+    for key in ("vocab", "width"):
+      v = getattr(self, key)
+      if not isinstance(v, int) or v <= 0:
+        raise ConfigError(f"{key} must be a positive integer, got {v!r}")
+    eps = self.norm.get("eps") if isinstance(self.norm, dict) else None
+    if not isinstance(eps, (int, float)) or not eps > 0:
+      raise ConfigError(f"norm.eps must be a positive number, got {eps!r}")
+    if not self.layers:
+      raise ConfigError("layers must list at least one layer")
+    for i in range(len(self.layers)):
+      self.mixer_of(i)
+      self.ff_of(i)
+    self.layer_order()
+
+  @property
+  def norm_eps(self) -> float:
+    return float(self.norm["eps"])
+
+  def layer_order(self) -> List[int]:
+    """The layers in the order they run: those of the loop ``times`` times in a row, then the rest."""
+    n = len(self.layers)
+    if self.loop is None:
+      return list(range(n))
+    if not isinstance(self.loop, dict):
+      raise ConfigError("loop must be an object with start, stop and times")
+    start, stop, times = (self.loop.get(k) for k in ("start", "stop", "times"))
+    for key, v in (("start", start), ("stop", stop), ("times", times)):
+      if not isinstance(v, int) or isinstance(v, bool) or v < 0:
+        raise ConfigError(f"loop.{key} must be a non-negative integer, got {v!r}")
+    if not (start <= stop <= n) or times < 1:
+      raise ConfigError(f"loop={self.loop!r} does not fit {n} layers (0 <= start <= stop <= layers, times >= 1)")
+    return list(range(start)) + list(range(start, stop)) * times + list(range(stop, n))
+
+  def type_of(self, i: int) -> str:
+    kind = self.layers[i].get("type")
+    if kind not in self.TYPES:
+      raise ConfigError(f"layers[{i}].type={kind!r} is not a mixer of this design (known: {', '.join(self.TYPES)})")
+    return kind
+
+  def mixer_of(self, i: int):
+    """The typed mixer configuration of layer ``i``: a ``LatentAttentionConfig``, a ``SelectiveScanConfig`` or, for a
+    ``parallel`` layer, the pair (``WindowedAttentionConfig``, ``GatedDeltaConfig``)."""
+    kind = self.type_of(i)
+    m = self.layers[i].get("mixer")
+    where = f"layers[{i}].mixer"
+    if not isinstance(m, dict):
+      raise ConfigError(f"{where} is missing")
+    if kind == "latent_attention":
+      c = LatentAttentionConfig(*(_positive_int(m, k, where) for k in ("heads", "dim", "rot_dim", "vdim", "q_rank", "kv_rank")),
+                                _number(m, "scale", where), RotationConfig.read(m, where))
+      if c.rot.dims != c.rot_dim:
+        raise ConfigError(f"{where}.rot.dims={c.rot.dims} must equal rot_dim={c.rot_dim}: the rotated part is rotated whole")
+      return c
+    if kind == "mamba1":
+      return SelectiveScanConfig(*(_positive_int(m, k, where) for k in ("inner", "state", "dt_rank", "conv")))
+    left, right = m.get("left"), m.get("right")
+    if not isinstance(left, dict) or not isinstance(right, dict):
+      raise ConfigError(f"{where} of a parallel layer needs 'left' and 'right'")
+    lw, rw = where + ".left", where + ".right"
+    mask = left.get("mask")
+    window, keep = None, 0
+    if mask is not None:
+      if not isinstance(mask, dict):
+        raise ConfigError(f"{lw}.mask must be an object")
+      window = _positive_int(mask, "size", lw + ".mask")
+      keep = mask.get("keep_first", 0)
+      if not isinstance(keep, int) or isinstance(keep, bool) or keep < 0:
+        raise ConfigError(f"{lw}.mask.keep_first must be a non-negative integer, got {keep!r}")
+    lc = WindowedAttentionConfig(*(_positive_int(left, k, lw) for k in ("heads", "kv_heads", "dim", "vdim")), _number(left, "scale", lw),
+                                 window, keep, RotationConfig.read(left, lw))
+    if lc.heads % lc.kv_heads:
+      raise ConfigError(f"{lw}.heads={lc.heads} must be a multiple of kv_heads={lc.kv_heads}")
+    if lc.vdim != lc.dim:
+      raise ConfigError(f"{lw}.vdim={lc.vdim} must equal dim={lc.dim}: the values are the keys")
+    if lc.rot.dims > lc.dim:
+      raise ConfigError(f"{lw}.rot.dims={lc.rot.dims} is more than dim={lc.dim}")
+    rc = GatedDeltaConfig(*(_positive_int(right, k, rw) for k in ("heads", "kv_heads", "dim", "vdim", "conv")))
+    if rc.heads % rc.kv_heads:
+      raise ConfigError(f"{rw}.heads={rc.heads} must be a multiple of kv_heads={rc.kv_heads}")
+    return lc, rc
+
+  def ff_of(self, i: int) -> Optional[int]:
+    """The width of layer ``i``'s dense feed-forward, or None for a layer without one."""
+    mlp = self.layers[i].get("mlp")
+    if mlp is None:
+      return None
+    if not isinstance(mlp, dict) or mlp.get("kind") != "dense":
+      raise ConfigError(f"layers[{i}].mlp.kind={mlp.get('kind') if isinstance(mlp, dict) else mlp!r} is not known (dense)")
+    return _positive_int(mlp, "ff", f"layers[{i}].mlp")
+
+  def low_rank(self, i: int, which: str, default: int = 16) -> int:
+    return int((self.low_ranks or {}).get(f"l{i}.{which}", default))
+
+  def read_tensor_shapes(self, shapes: Dict[str, tuple]) -> None:
+    ranks = dict(self.low_ranks or {})
+    for i in range(len(self.layers)):
+      if self.type_of(i) != "parallel":
+        continue
+      for which, tensor in (("decay", f"l{i}.mix.right.a1"), ("gate", f"l{i}.mix.right.g1")):
+        shape = shapes.get(tensor)
+        if shape is not None and len(shape) == 2:
+          ranks[f"l{i}.{which}"] = int(shape[0])
+    self.low_ranks = ranks or None
+
+  def to_dict(self) -> Dict[str, Any]:
+    d = {"architecture": self.architecture, "vocab": self.vocab, "width": self.width, "norm": dict(self.norm),
+         "layers": [dict(x) for x in self.layers]}
+    if self.loop is not None:
+      d["loop"] = dict(self.loop)
+    if self.low_ranks:
+      d["low_ranks"] = dict(self.low_ranks)
     d.update(self.extra)
     return d

@@ -72,7 +72,11 @@ def load_model_config(model_dir: str) -> ModelConfig:
   with open(path, encoding="utf-8") as f:
     d = json.load(f)
   config_cls, _ = lookup(architecture_of(d))
-  return config_cls.from_dict(d)
+  cfg = config_cls.from_dict(d)
+  if os.path.isdir(model_dir) and type(cfg).read_tensor_shapes is not ModelConfig.read_tensor_shapes:
+    from ..weights.loader import tensor_shapes      # the file's header only
+    cfg.read_tensor_shapes(tensor_shapes(model_dir))
+  return cfg
 
 
 def build_model_spec(config: ModelConfig):

@@ -84,7 +84,7 @@ struct DecodeArgs {
   float* part_o;                 // [n_dec, nh, max_splits, HD]
   float* part_ml;                // [n_dec, nh, max_splits, 2]
   int* counters;                 // [n_dec, nkv], zero between launches
-  int nh, nkv, page_size, window, chunk, max_splits;
+  int nh, nkv, page_size, window, chunk, max_splits, keep_first;
   float scale;
   const float* sink;             // [nh] or null
   const __nv_bfloat16* gate;     // [T, gate_stride], head h at h * out_hd; or null
@@ -137,11 +137,15 @@ decode_split_kernel(DecodeArgs a) {
   const int p = a.ctx_len[item] - 1;                       // position of the query token
   const int lo = a.window > 0 ? max(0, p - a.window + 1) : 0;
   const int c0 = lo / a.chunk;
-  const int n_splits = p / a.chunk - c0 + 1;
+  // the request's first keep_first keys that the window has passed are pieces of their own, ahead of the window's
+  const int kept = a.window > 0 ? min(a.keep_first, lo) : 0;
+  const int n_first = kept > 0 ? (kept - 1) / a.chunk + 1 : 0;
+  const int n_splits = n_first + p / a.chunk - c0 + 1;
   if (split >= n_splits) return;
-  const int chunk_idx = c0 + split;
-  const int k_begin = max(lo, chunk_idx * a.chunk);
-  const int k_end = min(p + 1, (chunk_idx + 1) * a.chunk);   // exclusive; the range is never empty
+  const int chunk_idx = split < n_first ? split : c0 + split - n_first;
+  const int k_begin = split < n_first ? chunk_idx * a.chunk : max(lo, chunk_idx * a.chunk);
+  const int k_end = split < n_first ? min(kept, (chunk_idx + 1) * a.chunk)
+                                    : min(p + 1, (chunk_idx + 1) * a.chunk);   // exclusive; the range is never empty
   const int nb = (k_end - k_begin + BK - 1) / BK;
   const int G = a.nh / a.nkv;
   const int row = a.q_start[item];
@@ -372,8 +376,9 @@ MI_API int mi_attention_decode_bf16(void* out, const void* q_base, int q_stride,
                                     const int* q_start, const int* ctx_len, const int* seq_slot, float* scratch,
                                     int* counters, int n_dec, int nh, int nkv, int page_size, float scale,
                                     int window, int chunk, int max_splits, const float* sink, const void* gate,
-                                    int gate_stride, int out_hd, cudaStream_t stream) {
+                                    int gate_stride, int out_hd, int keep_first, cudaStream_t stream) {
   MI_REQUIRE(out_hd > 0 && out_hd <= HD, "attention_decode: out_hd=%d must lie in 1..%d", out_hd, HD);
+  MI_REQUIRE(keep_first >= 0, "attention_decode: keep_first=%d must not be negative", keep_first);
   MI_REQUIRE(n_dec >= 0 && nh > 0 && nkv > 0 && nh % nkv == 0, "attention_decode: bad head counts nh=%d nkv=%d", nh, nkv);
   MI_REQUIRE(chunk >= BK && chunk <= MAX_CHUNK && chunk % BK == 0, "attention_decode: chunk=%d must be a multiple of %d up to %d", chunk, BK, MAX_CHUNK);
   MI_REQUIRE(max_splits >= 1 && max_splits <= 65535, "attention_decode: max_splits=%d", max_splits);
@@ -395,7 +400,7 @@ MI_API int mi_attention_decode_bf16(void* out, const void* q_base, int q_stride,
   a.part_o = scratch;
   a.part_ml = scratch + (size_t)n_dec * nh * max_splits * HD;
   a.counters = counters;
-  a.nh = nh; a.nkv = nkv; a.page_size = page_size; a.window = window; a.chunk = chunk; a.max_splits = max_splits;
+  a.nh = nh; a.nkv = nkv; a.page_size = page_size; a.window = window; a.chunk = chunk; a.max_splits = max_splits; a.keep_first = keep_first;
   a.scale = scale;
   a.sink = sink; a.gate = (const __nv_bfloat16*)gate; a.gate_stride = gate_stride; a.out_hd = out_hd;
   static bool configured = false;

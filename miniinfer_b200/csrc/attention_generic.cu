@@ -4,7 +4,7 @@
 // One warp per (token, query head).  The warp walks the keys the token may see - positions
 // max(0, p - window + 1) .. p of its own request, p being the token's position - in chunks of 32
 // aligned to multiples of 32, with an online softmax.  The order of the arithmetic depends on
-// (p, window) only, so the result for a token is bit-equal however the request was cut into steps
+// (p, window, keep_first) only, so the result for a token is bit-equal however the request was cut into steps
 // and whatever else is in the batch.  This is the attention of the 32-bit path, and the reference
 // against which the tensor-core kernels are checked on the device.
 //
@@ -19,7 +19,8 @@
 // exponential joins the softmax's denominator once, unscaled, with no key and no value (the running
 // maximum starts at the sink and the running sum at 1); an output gate - the output row is multiplied
 // element by element with sigmoid(gate[token, head, :]); and out_hd < head_dim - only the first out_hd
-// values of a head are written (the cache rows are padded).
+// values of a head are written (the cache rows are padded).  With a window, keep_first > 0 lets every token also see
+// the first keep_first keys of its request, at their true positions.
 #include "common.cuh"
 
 namespace {
@@ -66,7 +67,7 @@ attention_generic_kernel(T* __restrict__ out, const T* __restrict__ q_base, int 
                          const int* __restrict__ token_item, const int* __restrict__ positions,
                          const int* __restrict__ seq_slot, int nh, int nkv, int hd, int page_size,
                          float scale, int window, const float* __restrict__ sink, const T* __restrict__ gate,
-                         int gate_stride, int out_hd) {
+                         int gate_stride, int out_hd, int keep_first) {
   mi::grid_dependency_sync();
   __shared__ float qs[WARPS][MAX_HD];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -93,9 +94,13 @@ attention_generic_kernel(T* __restrict__ out, const T* __restrict__ q_base, int 
   float m = -INFINITY, l = 0.f;
   if (sink) { m = sink[head]; l = 1.f; }
 
-  for (int c = (lo / 32) * 32; c <= p; c += 32) {
+  // two stretches of keys: the request's first keep_first keys that the window has passed (none without a window),
+  // then the window itself; each in chunks of 32 aligned to multiples of 32
+  const int kept = window > 0 ? min(keep_first, lo) : 0;
+  for (int seg = kept > 0 ? 0 : 1; seg < 2; ++seg)
+  for (int c = seg ? (lo / 32) * 32 : 0; c <= (seg ? p : kept - 1); c += 32) {
     const int j = c + lane;
-    const bool valid = j >= lo && j <= p;
+    const bool valid = seg ? (j >= lo && j <= p) : j < kept;
     long long koff = -1;
     float s = -INFINITY;
     if (valid) {
@@ -143,7 +148,8 @@ MI_API int mi_attention_generic(void* out, const void* q_base, int q_stride, int
                                 const int* block_table, int bt_stride, const int* token_item,
                                 const int* positions, const int* seq_slot, int T, int nh, int nkv, int hd,
                                 int page_size, float scale, int window, const float* sink, const void* gate,
-                                int gate_stride, int out_hd, cudaStream_t stream) {
+                                int gate_stride, int out_hd, int keep_first, cudaStream_t stream) {
+  MI_REQUIRE(keep_first >= 0, "attention: keep_first=%d must not be negative", keep_first);
   MI_REQUIRE(out_hd > 0 && out_hd <= hd, "attention: out_hd=%d must lie in 1..head_dim", out_hd);
   MI_REQUIRE(T >= 0 && nh > 0 && nkv > 0 && nh % nkv == 0, "attention: bad head counts nh=%d nkv=%d", nh, nkv);
   MI_REQUIRE(hd > 0 && hd % 4 == 0 && hd <= MAX_HD, "attention: head_dim=%d must be a multiple of 4 up to %d", hd, MAX_HD);
@@ -155,11 +161,11 @@ MI_API int mi_attention_generic(void* out, const void* q_base, int q_stride, int
     mi::launch(attention_generic_kernel<__nv_bfloat16>, dim3(grid), dim3(WARPS * 32), 0, stream, 
         (__nv_bfloat16*)out, (const __nv_bfloat16*)q_base, q_stride, (const __nv_bfloat16*)kv_layer, block_table,
         bt_stride, token_item, positions, seq_slot, nh, nkv, hd, page_size, scale, window, sink, (const __nv_bfloat16*)gate,
-        gate_stride, out_hd);
+        gate_stride, out_hd, keep_first);
   else if (dtype == MI_F32)
     mi::launch(attention_generic_kernel<float>, dim3(grid), dim3(WARPS * 32), 0, stream, 
         (float*)out, (const float*)q_base, q_stride, (const float*)kv_layer, block_table, bt_stride, token_item,
-        positions, seq_slot, nh, nkv, hd, page_size, scale, window, sink, (const float*)gate, gate_stride, out_hd);
+        positions, seq_slot, nh, nkv, hd, page_size, scale, window, sink, (const float*)gate, gate_stride, out_hd, keep_first);
   else
     return mi_fail("attention: unknown dtype %d", dtype);
   MI_LAUNCH_OK("attention_generic");

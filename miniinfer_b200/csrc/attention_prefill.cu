@@ -83,7 +83,7 @@ struct PrefillArgs {
   const int* q_len;
   const int* ctx_len;
   const int* seq_slot;
-  int nh, nkv, page_size, window;
+  int nh, nkv, page_size, window, keep_first;
   float scale_log2;              // scale * log2(e)
   const float* sink;             // [nh] or null
   const __nv_bfloat16* gate;     // [T, gate_stride], head h at h * out_hd; or null
@@ -127,6 +127,9 @@ attention_prefill_kernel(PrefillArgs a) {
   const int p_last = p0 + rows - 1;
   const int lo_tile = a.window > 0 ? max(0, p0 - a.window + 1) : 0;
   const int kb_begin = lo_tile / BK, kb_end = p_last / BK;   // inclusive
+  // key blocks of the request's first keep_first keys that lie before the window's first block come first
+  const int n_first = (a.window > 0 && a.keep_first > 0) ? min((a.keep_first - 1) / BK + 1, kb_begin) : 0;
+  const int n_blocks = n_first + kb_end - kb_begin + 1;
   const int* bt = a.block_table + (size_t)a.seq_slot[item] * a.bt_stride;
   const size_t page_elems = (size_t)2 * a.nkv * a.page_size * HD;
   const size_t head_off = (size_t)kvh * a.page_size * HD;
@@ -139,7 +142,7 @@ attention_prefill_kernel(PrefillArgs a) {
     const __nv_bfloat16* src = valid ? a.q_base + (size_t)(row0 + r) * a.q_stride + (size_t)head * HD + c * 8 : a.q_base;
     cp_async16(qs + r * LDS + c * 8, src, valid);
   }
-  load_kv_block(kbuf, vbuf, a, bt, page_elems, head_off, v_off, kb_begin, p_last);
+  load_kv_block(kbuf, vbuf, a, bt, page_elems, head_off, v_off, n_first > 0 ? 0 : kb_begin, p_last);
   cp_async_commit();
 
   uint32_t qf[Q_IN_REGS ? KSTEPS : 1][4];
@@ -156,19 +159,21 @@ attention_prefill_kernel(PrefillArgs a) {
   const int lm = lane >> 3, lr = lane & 7;
   const __nv_bfloat16* q_lane = qs + (warp * 16 + (lm & 1) * 8 + lr) * LDS + (lm >> 1) * 8;
 
-  for (int kb = kb_begin; kb <= kb_end; ++kb) {
-    const int stage = (kb - kb_begin) & 1;
+  for (int bi = 0; bi < n_blocks; ++bi) {
+    const int kb = bi < n_first ? bi : kb_begin + (bi - n_first);
+    const int kb_next = bi + 1 < n_first ? bi + 1 : kb_begin + (bi + 1 - n_first);
+    const int stage = bi & 1;
     __nv_bfloat16* ks = kbuf + stage * BK * LDS;
     __nv_bfloat16* vs = vbuf + stage * BK * LDS;
-    if (kb < kb_end) {
-      load_kv_block(kbuf + (stage ^ 1) * BK * LDS, vbuf + (stage ^ 1) * BK * LDS, a, bt, page_elems, head_off, v_off, kb + 1, p_last);
+    if (bi + 1 < n_blocks) {
+      load_kv_block(kbuf + (stage ^ 1) * BK * LDS, vbuf + (stage ^ 1) * BK * LDS, a, bt, page_elems, head_off, v_off, kb_next, p_last);
       cp_async_commit();
       cp_async_wait<1>();
     } else {
       cp_async_wait<0>();
     }
     __syncthreads();
-    if (Q_IN_REGS && kb == kb_begin) {
+    if (Q_IN_REGS && bi == 0) {
 #pragma unroll
       for (int k = 0; k < (Q_IN_REGS ? KSTEPS : 1); ++k) ldmatrix_x4(qf[k], q_lane + k * 16);
     }
@@ -206,7 +211,7 @@ attention_prefill_kernel(PrefillArgs a) {
       for (int c = 0; c < 4; ++c) {
         const int j = kb * BK + i * 8 + 2 * t + (c & 1);
         const int h = c >> 1;
-        const bool see = row_ok[h] && j <= pr[h] && (a.window <= 0 || j > pr[h] - a.window);
+        const bool see = row_ok[h] && j <= pr[h] && (a.window <= 0 || j > pr[h] - a.window || j < a.keep_first);
         const float v = see ? s[i][c] * a.scale_log2 : -INFINITY;
         s[i][c] = v;
         mx[h] = fmaxf(mx[h], v);
@@ -300,7 +305,8 @@ MI_API int mi_attention_prefill_bf16(void* out, const void* q_base, int q_stride
                                      const int* block_table, int bt_stride, const int* tiles, int n_tiles,
                                      const int* q_start, const int* q_len, const int* ctx_len, const int* seq_slot,
                                      int nh, int nkv, int page_size, float scale, int window, const float* sink,
-                                     const void* gate, int gate_stride, int out_hd, cudaStream_t stream) {
+                                     const void* gate, int gate_stride, int out_hd, int keep_first, cudaStream_t stream) {
+  MI_REQUIRE(keep_first >= 0, "attention_prefill: keep_first=%d must not be negative", keep_first);
   MI_REQUIRE(out_hd > 0 && out_hd <= HD && out_hd % 2 == 0 && gate_stride % 2 == 0, "attention_prefill: out_hd=%d must be even, up to %d", out_hd, HD);
   MI_REQUIRE(n_tiles >= 0 && nh > 0 && nkv > 0 && nh % nkv == 0, "attention_prefill: bad head counts nh=%d nkv=%d", nh, nkv);
   MI_REQUIRE(page_size > 0 && q_stride % 8 == 0, "attention_prefill: bad page_size=%d or q_stride=%d", page_size, q_stride);
@@ -315,7 +321,7 @@ MI_API int mi_attention_prefill_bf16(void* out, const void* q_base, int q_stride
   a.bt_stride = bt_stride;
   a.tiles = tiles;
   a.q_start = q_start; a.q_len = q_len; a.ctx_len = ctx_len; a.seq_slot = seq_slot;
-  a.nh = nh; a.nkv = nkv; a.page_size = page_size; a.window = window;
+  a.nh = nh; a.nkv = nkv; a.page_size = page_size; a.window = window; a.keep_first = keep_first;
   a.scale_log2 = scale * 1.4426950408889634f;
   a.sink = sink; a.gate = (const __nv_bfloat16*)gate; a.gate_stride = gate_stride; a.out_hd = out_hd;
   const size_t smem = (size_t)(BQ + 4 * BK) * LDS * sizeof(__nv_bfloat16);

@@ -16,9 +16,10 @@ cublasHandle_t handles[MAX_DEVICES] = {};
 
 }  // namespace
 
-MI_API int mi_gemm_cublas_bf16(void* out, int out_dtype, const void* x, const void* w, int M, int N, int K,
+// lda: elements between two rows of x (K for packed rows; more when x is a column range of wider rows).
+MI_API int mi_gemm_cublas_bf16(void* out, int out_dtype, const void* x, const void* w, int M, int N, int K, int lda,
                                cudaStream_t stream) {
-  MI_REQUIRE(M >= 0 && N > 0 && K > 0, "gemm_cublas: bad sizes M=%d N=%d K=%d", M, N, K);
+  MI_REQUIRE(M >= 0 && N > 0 && K > 0 && lda >= K, "gemm_cublas: bad sizes M=%d N=%d K=%d lda=%d", M, N, K, lda);
   MI_REQUIRE(out_dtype == MI_BF16 || out_dtype == MI_F32, "gemm_cublas: unknown output dtype %d", out_dtype);
   if (M == 0) return 0;
   int dev = 0;
@@ -36,7 +37,7 @@ MI_API int mi_gemm_cublas_bf16(void* out, int out_dtype, const void* x, const vo
   if (st != CUBLAS_STATUS_SUCCESS) return mi_fail("gemm_cublas: cublasSetStream failed with status %d", (int)st);
   // Row-major out[M, N] is column-major out^T[N, M] = w (as K x N column-major, transposed) * x (K x M).
   const float alpha = 1.f, beta = 0.f;
-  st = cublasGemmEx(h, CUBLAS_OP_T, CUBLAS_OP_N, N, M, K, &alpha, w, CUDA_R_16BF, K, x, CUDA_R_16BF, K, &beta, out,
+  st = cublasGemmEx(h, CUBLAS_OP_T, CUBLAS_OP_N, N, M, K, &alpha, w, CUDA_R_16BF, K, x, CUDA_R_16BF, lda, &beta, out,
                     out_dtype == MI_BF16 ? CUDA_R_16BF : CUDA_R_32F, N, CUBLAS_COMPUTE_32F, CUBLAS_GEMM_DEFAULT);
   if (st != CUBLAS_STATUS_SUCCESS) return mi_fail("gemm_cublas: cublasGemmEx failed with status %d (M=%d N=%d K=%d)", (int)st, M, N, K);
   return 0;

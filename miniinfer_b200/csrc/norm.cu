@@ -131,6 +131,106 @@ MI_API int mi_add_rmsnorm(void* out, int out_dtype, float* resid, const void* de
 }
 
 // ------------------------------------------------------------------------------------------------
+// One root mean square, two weights: blocks whose mixer and feed-forward each have a norm of their own on the same
+// residual rows.  sum = resid[row] (+ d1[row]) (+ d2[row]); out1 = w1 * sum * rstd; out2 = w2 * sum * rstd (if asked for).
+// Also the plain RMSNorm behind a block that leaves two outputs pending (out2 null).
+namespace {
+
+template <typename TOut, typename TDelta>
+__global__ void __launch_bounds__(256)
+add_rmsnorm_pair_kernel(TOut* __restrict__ out1, TOut* __restrict__ out2, float* __restrict__ resid,
+                        const TDelta* __restrict__ d1, const TDelta* __restrict__ d2, const float* __restrict__ w1,
+                        const float* __restrict__ w2, const int* __restrict__ rows, int H, float eps, int write_back) {
+  __shared__ float scratch[33];
+  const int r = blockIdx.x;
+  const int row = rows ? rows[r] : r;
+  mi::grid_dependency_sync();
+  float* x = resid + (size_t)row * H;
+  const TDelta* a = d1 ? d1 + (size_t)row * H : nullptr;
+  const TDelta* b = d2 ? d2 + (size_t)row * H : nullptr;
+  const bool any = a || b;
+  float ss = 0.f;
+  for (int h = threadIdx.x; h < H; h += blockDim.x) {
+    float v = x[h];
+    if (a && b) v += mi::to_float(a[h]) + mi::to_float(b[h]);     // the two outputs first, then the stream
+    else if (a) v += mi::to_float(a[h]);
+    else if (b) v += mi::to_float(b[h]);
+    if (write_back && any) x[h] = v;
+    ss += v * v;
+  }
+  const float total = mi::block_sum(ss, scratch);
+  const float rstd = 1.f / sqrtf(total / (float)H + eps);
+  for (int h = threadIdx.x; h < H; h += blockDim.x) {
+    float v = x[h];
+    if (any && !write_back) {
+      if (a && b) v += mi::to_float(a[h]) + mi::to_float(b[h]);
+      else if (a) v += mi::to_float(a[h]);
+      else v += mi::to_float(b[h]);
+    }
+    const float n = v * rstd;
+    out1[(size_t)r * H + h] = mi::from_float<TOut>(w1[h] * n);
+    if (out2) out2[(size_t)r * H + h] = mi::from_float<TOut>(w2[h] * n);
+  }
+}
+
+// out = scale * (w1 * a / rms(a) + w2 * b / rms(b)), each row normalised by its own root mean square: the meeting
+// of two mixers that ran side by side on the same input.
+template <typename T>
+__global__ void __launch_bounds__(256)
+rms_pair_sum_kernel(T* __restrict__ out, const T* __restrict__ a, const T* __restrict__ b, const float* __restrict__ w1,
+                    const float* __restrict__ w2, int H, float eps, float scale) {
+  __shared__ float scratch[33];
+  const int r = blockIdx.x;
+  mi::grid_dependency_sync();
+  const T* x = a + (size_t)r * H;
+  const T* y = b + (size_t)r * H;
+  float sa = 0.f, sb = 0.f;
+  for (int h = threadIdx.x; h < H; h += blockDim.x) {
+    const float u = mi::to_float(x[h]), v = mi::to_float(y[h]);
+    sa += u * u;
+    sb += v * v;
+  }
+  const float ta = mi::block_sum(sa, scratch);
+  const float tb = mi::block_sum(sb, scratch);
+  const float ra = 1.f / sqrtf(ta / (float)H + eps), rb = 1.f / sqrtf(tb / (float)H + eps);
+  for (int h = threadIdx.x; h < H; h += blockDim.x)
+    out[(size_t)r * H + h] = mi::from_float<T>(scale * (w1[h] * (mi::to_float(x[h]) * ra) + w2[h] * (mi::to_float(y[h]) * rb)));
+}
+
+}  // namespace
+
+MI_API int mi_add_rmsnorm_pair(void* out1, void* out2, int out_dtype, float* resid, const void* d1, const void* d2, int delta_dtype,
+                               const float* w1, const float* w2, const int* rows, int R, int H, float eps, int write_back,
+                               cudaStream_t stream) {
+  MI_REQUIRE(R >= 0 && H > 0 && eps > 0.f, "rmsnorm_pair: bad sizes R=%d H=%d or eps", R, H);
+  MI_REQUIRE(out1 != nullptr && w1 != nullptr && (out2 == nullptr || w2 != nullptr), "rmsnorm_pair: an output without its weight");
+  if (R == 0) return 0;
+#define MI_NORM_LAUNCH(TO, TD) \
+  mi::launch(add_rmsnorm_pair_kernel<TO, TD>, dim3(R), dim3(256), 0, stream, (TO*)out1, (TO*)out2, resid, (const TD*)d1, (const TD*)d2, w1, w2, rows, H, eps, write_back)
+  if (out_dtype == MI_BF16 && delta_dtype == MI_BF16) MI_NORM_LAUNCH(__nv_bfloat16, __nv_bfloat16);
+  else if (out_dtype == MI_F32 && delta_dtype == MI_F32) MI_NORM_LAUNCH(float, float);
+  else if (out_dtype == MI_BF16 && delta_dtype == MI_F32) MI_NORM_LAUNCH(__nv_bfloat16, float);
+  else if (out_dtype == MI_F32 && delta_dtype == MI_BF16) MI_NORM_LAUNCH(float, __nv_bfloat16);
+  else return mi_fail("rmsnorm_pair: unknown dtypes out=%d delta=%d", out_dtype, delta_dtype);
+#undef MI_NORM_LAUNCH
+  MI_LAUNCH_OK("add_rmsnorm_pair");
+  return 0;
+}
+
+MI_API int mi_rms_pair_sum(void* out, const void* a, const void* b, int dtype, const float* w1, const float* w2, int R, int H,
+                           float eps, float scale, cudaStream_t stream) {
+  MI_REQUIRE(R >= 0 && H > 0 && eps > 0.f, "rms_pair_sum: bad sizes R=%d H=%d or eps", R, H);
+  if (R == 0) return 0;
+  if (dtype == MI_BF16)
+    mi::launch(rms_pair_sum_kernel<__nv_bfloat16>, dim3(R), dim3(256), 0, stream, (__nv_bfloat16*)out, (const __nv_bfloat16*)a, (const __nv_bfloat16*)b, w1, w2, H, eps, scale);
+  else if (dtype == MI_F32)
+    mi::launch(rms_pair_sum_kernel<float>, dim3(R), dim3(256), 0, stream, (float*)out, (const float*)a, (const float*)b, w1, w2, H, eps, scale);
+  else return mi_fail("rms_pair_sum: unknown dtype %d", dtype);
+  MI_LAUNCH_OK("rms_pair_sum");
+  return 0;
+}
+
+// ------------------------------------------------------------------------------------------------
 // Layer norm (mean and variance, weight and bias) with the residual add in front of it.
 //
 //   sum[r, :] = resid[row(r), :] + (d1[row(r), :] + d2[row(r), :])      float32; d1, d2 optional

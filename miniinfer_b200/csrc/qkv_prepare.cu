@@ -1,9 +1,11 @@
-// From the rows of a fused query / key / value product to what attention reads, for mixers whose heads
-// are not rotated: one pass over a token's heads that
+// From the rows of a fused query / key / value product to what attention reads: one pass over a token's heads that
 //
 //   * divides each query and key head by its root mean square over the head, x / sqrt(mean(x^2) + eps),
 //     in float32 (optionally times a weight per dimension), and writes the query heads, padded with
 //     zeros to the cache's head size, into a packed buffer [token, head, cache head size];
+//   * optionally rotates the first rot_dims values of each query and key head, after the norm, by the angles of the
+//     token's position (a table row: cos of rot_dims / 2 angles, then their sines): value i pairs with value
+//     i + rot_dims / 2 (halves) or value 2i with 2i + 1 (interleaved); (u, v) -> (u cos - v sin, v cos + u sin);
 //   * mixes the token's value heads with the values another layer made for the same token,
 //     v <- (1 - lambda) v + lambda v_other (lambda read from the device), or records them as that
 //     other layer's values (v_mode 1), or leaves them alone (v_mode 0);
@@ -36,13 +38,18 @@ struct PrepArgs {
   const int* slot_mapping;  // null: nothing is stored
   T* kv_layer;            // [page, 2, nkv, page_size, hdp]
   int page_size;
+  const float* rope;      // [positions, rot_dims] or null: no rotation
+  const int* positions;   // [tokens]
+  int rot_dims, interleaved;
 };
 
 template <typename T>
 __global__ void __launch_bounds__(PREP_WARPS * 32)
 qkv_prepare_kernel(PrepArgs<T> a) {
+  __shared__ float stage[PREP_WARPS][32 * PREP_MAX_PER_LANE];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int tkn = blockIdx.x;
+  const int pos = a.rope ? a.positions[tkn] : 0;
   const float lam = (a.v_mode == 2) ? *a.lambda : 0.f;       // a weight: no kernel writes it
   const int slot = a.slot_mapping ? a.slot_mapping[tkn] : -1;  // part of the step's description
   mi::grid_dependency_sync();
@@ -69,7 +76,40 @@ qkv_prepare_kernel(PrepArgs<T> a) {
       T* dst = nullptr;
       if (is_q) dst = a.q_out + ((size_t)tkn * a.nh + h) * a.hdp;
       else if (slot >= 0) dst = a.kv_layer + ((((size_t)page * 2 + 0) * a.nkv + h) * a.page_size + off) * a.hdp;
-      if (dst) {
+      if (a.rope) {
+        // the normalised head through shared memory, so that every value meets its partner
+        float* sh = stage[warp];
+        const float* cs = a.rope + (size_t)pos * a.rot_dims;
+        const int half = a.rot_dims / 2;
+#pragma unroll
+        for (int i = 0; i < PREP_MAX_PER_LANE; ++i) {
+          const int d = lane + 32 * i;
+          float y = v[i] * r;
+          if (w && d < a.dim) y *= w[d];
+          v[i] = y;
+          if (d < a.dim) sh[d] = y;
+        }
+        __syncwarp();
+#pragma unroll
+        for (int i = 0; i < PREP_MAX_PER_LANE; ++i) {
+          const int d = lane + 32 * i;
+          if (d < a.rot_dims) {
+            const bool first = a.interleaved ? !(d & 1) : d < half;
+            const int pi = a.interleaved ? d >> 1 : (first ? d : d - half);
+            const int partner = a.interleaved ? d ^ 1 : (first ? d + half : d - half);
+            const float c = cs[pi], sn = cs[half + pi], other = sh[partner];
+            v[i] = first ? v[i] * c - other * sn : v[i] * c + other * sn;
+          }
+        }
+        __syncwarp();
+        if (dst) {
+#pragma unroll
+          for (int i = 0; i < PREP_MAX_PER_LANE; ++i) {
+            const int d = lane + 32 * i;
+            if (d < a.hdp) dst[d] = mi::from_float<T>(d < a.dim ? v[i] : 0.f);
+          }
+        }
+      } else if (dst) {
 #pragma unroll
         for (int i = 0; i < PREP_MAX_PER_LANE; ++i) {
           const int d = lane + 32 * i;
@@ -187,7 +227,10 @@ qkv_prepare_pairs_kernel(PrepArgs<T> a) {
 MI_API int mi_qkv_norm_mix_store(const void* proj, int dtype, int proj_stride, int q_off, int k_off, int v_off, int T, int nh,
                                  int nkv, int dim, int vdim, int hdp, void* q_out, const float* q_w, const float* k_w,
                                  float eps, int normalise, const float* lambda, void* v_other, int v_mode,
-                                 const int* slot_mapping, void* kv_layer, int page_size, cudaStream_t stream) {
+                                 const int* slot_mapping, void* kv_layer, int page_size, const float* rope, const int* positions,
+                                 int rot_dims, int interleaved, cudaStream_t stream) {
+  MI_REQUIRE(rope == nullptr || (positions != nullptr && rot_dims > 0 && rot_dims % 2 == 0 && rot_dims <= dim),
+             "qkv_prepare: a rotation needs positions and an even number of rotated values, at most dim=%d (got %d)", dim, rot_dims);
   MI_REQUIRE(T >= 0 && nh > 0 && nkv > 0 && dim > 0 && vdim > 0 && nh + 2 * nkv <= 4 * 65535, "qkv_prepare: bad sizes");
   MI_REQUIRE(hdp >= dim && hdp >= vdim && hdp <= 32 * PREP_MAX_PER_LANE, "qkv_prepare: cache head size %d must cover dim=%d and vdim=%d, up to %d",
              hdp, dim, vdim, 32 * PREP_MAX_PER_LANE);
@@ -196,7 +239,7 @@ MI_API int mi_qkv_norm_mix_store(const void* proj, int dtype, int proj_stride, i
   MI_REQUIRE(slot_mapping == nullptr || (kv_layer != nullptr && page_size > 0), "qkv_prepare: a store needs the cache layer");
   if (T == 0) return 0;
   const size_t es = dtype == MI_BF16 ? 2 : 4;
-  const bool pairs = dim % 2 == 0 && vdim % 2 == 0 && hdp % 2 == 0 && proj_stride % 2 == 0 && q_off % 2 == 0 && k_off % 2 == 0 && v_off % 2 == 0 &&
+  const bool pairs = rope == nullptr && dim % 2 == 0 && vdim % 2 == 0 && hdp % 2 == 0 && proj_stride % 2 == 0 && q_off % 2 == 0 && k_off % 2 == 0 && v_off % 2 == 0 &&
                      ((uintptr_t)proj % (2 * es)) == 0 && ((uintptr_t)q_out % (2 * es)) == 0 && ((uintptr_t)kv_layer % (2 * es)) == 0 &&
                      ((uintptr_t)v_other % (2 * es)) == 0;
 #define MI_PREP(TT)                                                                                          \
@@ -206,6 +249,7 @@ MI_API int mi_qkv_norm_mix_store(const void* proj, int dtype, int proj_stride, i
     a.nh = nh; a.nkv = nkv; a.dim = dim; a.vdim = vdim; a.hdp = hdp; a.q_out = (TT*)q_out; a.q_w = q_w; a.k_w = k_w; \
     a.eps = eps; a.normalise = normalise; a.lambda = lambda; a.v_other = (TT*)v_other; a.v_mode = v_mode;     \
     a.slot_mapping = slot_mapping; a.kv_layer = (TT*)kv_layer; a.page_size = page_size;                      \
+    a.rope = rope; a.positions = positions; a.rot_dims = rot_dims; a.interleaved = interleaved;              \
     if (pairs) mi::launch(qkv_prepare_pairs_kernel<TT>, dim3(T, (nh + 2 * nkv + PREP_WARPS - 1) / PREP_WARPS), dim3(PREP_WARPS * 32), 0, stream, a); \
     else mi::launch(qkv_prepare_kernel<TT>, dim3(T, (nh + 2 * nkv + PREP_WARPS - 1) / PREP_WARPS), dim3(PREP_WARPS * 32), 0, stream, a);                        \
   } while (0)

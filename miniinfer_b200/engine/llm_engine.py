@@ -21,7 +21,7 @@ import numpy as np
 import torch
 
 from ..cache.manager import KVCacheManager
-from ..cache.specs import PagedKVSpec
+from ..cache.specs import PagedKVSpec, flatten_specs
 from ..config import EngineConfig, build_model_spec, load_model_config
 from ..sampling import Sampler, SamplingParams, derive_seed
 from ..utils.crash_dump import dump_step_failure
@@ -46,13 +46,13 @@ def size_cache_pages(layer_specs, page_size: int, dtype: torch.dtype, device: to
   if device.type != "cuda":
     return cap
   free, total = torch.cuda.mem_get_info(device)
-  usable = int((free - (1.0 - utilization) * total) * 0.9)
+  usable = int((free - (1.0 - utilization) * total) * 0.9) - KVCacheManager.state_bytes(layer_specs, max_num_seqs)
   per_page = KVCacheManager.bytes_per_page(layer_specs, page_size, dtype, windowed=False)
   if max_step_tokens is None:
     per_page = KVCacheManager.bytes_per_page(layer_specs, page_size, dtype)
   else:
     size = torch.empty((), dtype=dtype).element_size()
-    for spec in layer_specs:
+    for spec in flatten_specs(layer_specs):
       if isinstance(spec, PagedKVSpec) and spec.window is not None:
         pages = KVCacheManager.group_pages(spec, page_size, cap, max_num_seqs, max_step_tokens) + 1
         usable -= pages * 2 * spec.num_kv_heads * spec.head_dim * page_size * size

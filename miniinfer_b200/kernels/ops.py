@@ -232,6 +232,22 @@ def linear(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, force_skinny: bo
   if M == 0:
     return
   lib = common_lib()
+  if not x.is_contiguous() or (x.dtype == torch.bfloat16 and (K % 8 != 0 or x.data_ptr() % 16 != 0 or w.data_ptr() % 16 != 0)):
+    # x is a column range of wider rows, or its rows cannot be read 16 bytes at a time: the library product for many
+    # bfloat16 rows, else the product that takes any strides and sizes
+    if x.dim() != 2 or x.stride(1) != 1 or x.dtype != w.dtype:
+      raise KernelError("linear: x must have contiguous rows of the weights' dtype")
+    lda = int(x.stride(0))
+    if (x.dtype == torch.bfloat16 and M > SKINNY_BEST_M and K % 8 == 0 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0
+        and out.dtype in (torch.bfloat16, torch.float32) and out.is_contiguous()):
+      if not _capturing:
+        _check(lib, lib.mi_gemm_cublas_bf16(_ptr(out), _dt(out), ctypes.c_void_p(x.data_ptr()), _ptr(w), M, N, K, lda, _stream()), kernels=0)
+        return
+      if out.dtype == torch.bfloat16:
+        torch.mm(x, _transposed(w), out=out)
+        return
+    linear_batched(out.unsqueeze(1), x.unsqueeze(1), w.unsqueeze(0))
+    return
   if x.dtype == torch.float32:
     _check(lib, lib.mi_gemm_f32(_ptr(out, torch.float32), _ptr(x), _ptr(w, torch.float32), M, N, K, N, _stream()))
     return
@@ -253,7 +269,7 @@ def linear(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, force_skinny: bo
       raise KernelError(f"linear: K={K} must be a multiple of 8 (16-byte loads of bf16 rows)")
     if not _capturing and out.dtype in (torch.bfloat16, torch.float32):
       # more than 16 rows: straight to cuBLAS (a third of the host time of torch.mm); not while a graph is recorded
-      _check(lib, lib.mi_gemm_cublas_bf16(_ptr(out), _dt(out), _ptr(x), _ptr(w), M, N, K, _stream()), kernels=0)
+      _check(lib, lib.mi_gemm_cublas_bf16(_ptr(out), _dt(out), _ptr(x), _ptr(w), M, N, K, K, _stream()), kernels=0)
       return
     if out.dtype == torch.bfloat16:
       torch.mm(x, _transposed(w), out=out)
@@ -383,13 +399,18 @@ def qkv_norm_mix_store(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, q
                        num_kv_heads: int, dim: int, vdim: int, eps: float, normalise: bool = True,
                        q_weight: Optional[torch.Tensor] = None, k_weight: Optional[torch.Tensor] = None,
                        mix: Optional[torch.Tensor] = None, v_other: Optional[torch.Tensor] = None, v_mode: int = 0,
-                       slot_mapping: Optional[torch.Tensor] = None, kv_layer: Optional[torch.Tensor] = None) -> None:
+                       slot_mapping: Optional[torch.Tensor] = None, kv_layer: Optional[torch.Tensor] = None,
+                       rope: Optional[torch.Tensor] = None, positions: Optional[torch.Tensor] = None,
+                       interleaved: bool = False) -> None:
   """From the rows of a fused projection (queries at column ``q_off``, keys at ``k_off``, values at ``v_off``) to what
   attention reads, for heads that are not rotated: query and key heads divided by their root mean square over
   ``dim`` (x / sqrt(mean(x^2) + eps), float32; times ``q_weight`` / ``k_weight`` if given); queries into
   ``q_out [tokens, heads, cache head size]`` padded with zeros; values mixed with another layer's values of the same
   token (``v_mode`` 2: v <- (1 - mix) v + mix v_other, ``mix`` a scalar on the device), recorded as those values
-  (``v_mode`` 1) or left alone (0); keys and values stored into the layer's pages at ``slot_mapping``."""
+  (``v_mode`` 1) or left alone (0); keys and values stored into the layer's pages at ``slot_mapping``.
+  ``rope [positions, rot_dims]`` float32 (cos of rot_dims / 2 angles, then their sines): the first ``rot_dims`` values of
+  every query and key head are rotated, after the norm, by the angles of the token's position - value i with value
+  i + rot_dims / 2, or 2i with 2i + 1 if ``interleaved``.  ``v_off == k_off`` makes the values the keys as projected."""
   lib = common_lib()
   T = proj.shape[0]
   hdp = q_out.shape[1] // num_heads
@@ -412,7 +433,185 @@ def qkv_norm_mix_store(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, q
     ctypes.c_float(eps), int(bool(normalise)), _ptr(mix, torch.float32) if mix is not None else none,
     _ptr(v_other) if v_other is not None else none, int(v_mode),
     _ptr(slot_mapping, torch.int32) if (slot_mapping is not None and kv_layer is not None) else none,
-    _ptr(kv_layer) if kv_layer is not None else none, page_size, _stream()))
+    _ptr(kv_layer) if kv_layer is not None else none, page_size,
+    _ptr(rope, torch.float32) if rope is not None else none, _ptr(positions, torch.int32) if rope is not None else none,
+    int(rope.shape[1]) if rope is not None else 0, int(bool(interleaved)), _stream()))
+
+
+def add_rmsnorm_pair(out1: torch.Tensor, out2: Optional[torch.Tensor], resid: torch.Tensor, delta: Optional[torch.Tensor],
+                     delta2: Optional[torch.Tensor], w1: torch.Tensor, w2: Optional[torch.Tensor], eps: float,
+                     rows: Optional[torch.Tensor] = None, write_back: bool = True) -> None:
+  """s = resid[row] + (delta[row] + delta2[row]) (both optional, of one dtype); out1[r] = w1 * s / rms(s) and, if asked
+  for, out2[r] = w2 * s / rms(s), rms(s) = sqrt(mean(s^2) + eps); the sum goes back to resid if write_back.  float32."""
+  lib = common_lib()
+  R, H = out1.shape
+  if resid.shape[1] != H or w1.shape != (H,) or (out2 is not None and (w2 is None or w2.shape != (H,) or out2.shape != out1.shape or out2.dtype != out1.dtype)):
+    raise KernelError("add_rmsnorm_pair: shapes do not match")
+  for d in (delta, delta2):
+    if d is not None and d.shape != resid.shape:
+      raise KernelError("add_rmsnorm_pair: a delta differs from the residual in shape")
+  if delta is not None and delta2 is not None and delta.dtype != delta2.dtype:
+    raise KernelError("add_rmsnorm_pair: the two deltas differ in dtype")
+  if (rows is None and resid.shape[0] != R) or (rows is not None and rows.shape[0] != R):
+    raise KernelError("add_rmsnorm_pair: out, rows and resid differ in rows")
+  first = delta if delta is not None else delta2
+  _check(lib, lib.mi_add_rmsnorm_pair(_ptr(out1), _ptr(out2), _dt(out1), _ptr(resid, torch.float32), _ptr(delta), _ptr(delta2),
+                                      _dt(first) if first is not None else F32, _ptr(w1, torch.float32),
+                                      _ptr(w2, torch.float32) if w2 is not None else _ptr(None),
+                                      _ptr(rows, torch.int32) if rows is not None else _ptr(None), R, H, ctypes.c_float(eps),
+                                      int(bool(write_back)), _stream()))
+
+
+def rms_pair_sum(out: torch.Tensor, a: torch.Tensor, b: torch.Tensor, w1: torch.Tensor, w2: torch.Tensor, eps: float, scale: float) -> None:
+  """out = scale * (w1 * a / rms(a) + w2 * b / rms(b)) row by row, rms(x) = sqrt(mean(x^2) + eps), in float32."""
+  lib = common_lib()
+  R, H = out.shape
+  if a.shape != (R, H) or b.shape != (R, H) or w1.shape != (H,) or w2.shape != (H,) or a.dtype != out.dtype or b.dtype != out.dtype:
+    raise KernelError("rms_pair_sum: shapes or dtypes do not match")
+  _check(lib, lib.mi_rms_pair_sum(_ptr(out), _ptr(a), _ptr(b), _dt(out), _ptr(w1, torch.float32), _ptr(w2, torch.float32), R, H,
+                                  ctypes.c_float(eps), ctypes.c_float(scale), _stream()))
+
+
+def _cols(t: torch.Tensor, what: str):
+  """(pointer, row stride) of a 2-d operand that may be a column range of wider contiguous rows."""
+  if t.dim() != 2 or t.stride(1) != 1 or not t.is_cuda:
+    raise KernelError(f"{what}: operands must be CUDA matrices with contiguous rows")
+  return ctypes.c_void_p(t.data_ptr()), int(t.stride(0))
+
+
+def linear_batched(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None, softplus: bool = False,
+                   row_gate: Optional[torch.Tensor] = None) -> None:
+  """out[:, b, :] = x[:, b, :] @ w[b]^T for ``x [M, batch, K]``, ``w [batch, N, K]``, ``out [M, batch, N]`` - views whose
+  strides may be anything as long as the last axis is contiguous (the heads of a token's row, a column range of a
+  row); float32 sums, k ascending.  ``bias [N]`` float32 is added, ``softplus`` applied, and with ``row_gate [M, >= batch]``
+  (one logit per row and batch) the result is multiplied with its sigmoid."""
+  lib = common_lib()
+  M, B, K = x.shape
+  N = w.shape[1]
+  if w.shape != (B, N, K) or out.shape != (M, B, N) or x.dtype != w.dtype:
+    raise KernelError(f"linear_batched: shapes do not match: x {tuple(x.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
+  for t in (x, w, out):
+    if t.stride(2) != 1 or not t.is_cuda:
+      raise KernelError("linear_batched: the last axis of every operand must be contiguous, on a CUDA device")
+  if M == 0:
+    return
+  gate_stride = 0
+  if row_gate is not None:
+    if row_gate.dim() != 2 or row_gate.shape[0] != M or row_gate.shape[1] < B or row_gate.stride(1) != 1 or row_gate.dtype != x.dtype:
+      raise KernelError("linear_batched: the row gate must hold a logit per row and batch, in the operands' dtype")
+    gate_stride = row_gate.stride(0)
+  _check(lib, lib.mi_gemm_batched(
+    ctypes.c_void_p(out.data_ptr()), _dt(out), ctypes.c_void_p(x.data_ptr()), ctypes.c_void_p(w.data_ptr()), _dt(x), B, M, N, K,
+    int(x.stride(0)), ctypes.c_longlong(x.stride(1)), int(w.stride(1)), ctypes.c_longlong(w.stride(0)),
+    int(out.stride(0)), ctypes.c_longlong(out.stride(1)), _ptr(bias, torch.float32) if bias is not None else _ptr(None),
+    int(bool(softplus)), ctypes.c_void_p(row_gate.data_ptr()) if row_gate is not None else _ptr(None), gate_stride, _stream()))
+
+
+def causal_conv(out: torch.Tensor, x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], state: torch.Tensor,
+                ctx, silu: bool = True) -> None:
+  """Short causal convolution over time per channel with the activation behind it, continuing from and updating the
+  per-request state: ``out[t, c] = act(bias[c] + sum_k weight[c, taps - 1 - k] * x[t - k, c])``.  ``x`` and ``out`` may be
+  column ranges of wider rows; ``state [slots, >= (taps - 1) * channels]`` float32 holds each request's last taps - 1
+  inputs (oldest first) and is brought up to date after the convolution (two launches)."""
+  lib = common_lib()
+  T, C = x.shape
+  taps = weight.shape[1]
+  if weight.shape != (C, taps) or out.shape != (T, C) or out.dtype != x.dtype or (bias is not None and bias.shape != (C,)):
+    raise KernelError("causal_conv: shapes do not match")
+  if state.dim() != 2 or state.stride(1) != 1 or state.dtype != torch.float32:
+    raise KernelError("causal_conv: the state must be float32 rows, one per request slot")
+  xp, ldx = _cols(x, "causal_conv")
+  op, ldo = _cols(out, "causal_conv")
+  _check(lib, lib.mi_causal_conv(op, ldo, xp, ldx, _dt(x), _ptr(weight, torch.float32), _ptr(bias, torch.float32) if bias is not None else _ptr(None),
+                                 ctypes.c_void_p(state.data_ptr()), ctypes.c_longlong(state.stride(0)), _ptr(ctx.token_item, torch.int32),
+                                 _ptr(ctx.q_start, torch.int32), _ptr(ctx.q_len, torch.int32), _ptr(ctx.seq_slot, torch.int32),
+                                 T, ctx.num_items, C, taps, int(bool(silu)), _stream()), kernels=2 if taps > 1 else 1)
+
+
+def selective_scan(y: torch.Tensor, u: torch.Tensor, dt_in: torch.Tensor, bc: torch.Tensor, b_off: int, c_off: int, z: torch.Tensor,
+                   dt_bias: torch.Tensor, A_log: torch.Tensor, D: torch.Tensor, state: torch.Tensor, ctx) -> None:
+  """The selective scan over each item's new tokens, from and to the per-request state ``[slots, >= inner * N]`` float32:
+  ``dt = softplus(dt_in + dt_bias)``, ``S[c, n] <- exp(dt_c A[c, n]) S[c, n] + dt_c u_c B_n`` with ``A = -exp(A_log)``,
+  ``y_c = (sum_n S[c, n] C_n + D_c u_c) * silu(z_c)``; B and C are ``N`` columns of ``bc`` from ``b_off`` / ``c_off``."""
+  lib = common_lib()
+  T, inner = u.shape
+  N = A_log.shape[1]
+  if A_log.shape != (inner, N) or dt_bias.shape != (inner,) or D.shape != (inner,) or y.shape != (T, inner) or dt_in.shape != (T, inner) or z.shape != (T, inner):
+    raise KernelError("selective_scan: shapes do not match")
+  if bc.shape[0] != T or max(b_off, c_off) + N > bc.shape[1] or len({y.dtype, u.dtype, dt_in.dtype, bc.dtype, z.dtype}) != 1:
+    raise KernelError("selective_scan: the B / C rows do not match, or the activations differ in dtype")
+  if state.dim() != 2 or state.stride(1) != 1 or state.dtype != torch.float32:
+    raise KernelError("selective_scan: the state must be float32 rows, one per request slot")
+  (yp, ldy), (up, ldu), (dp, ldd), (bp, ldb), (zp, ldz) = (_cols(t, "selective_scan") for t in (y, u, dt_in, bc, z))
+  _check(lib, lib.mi_selective_scan(yp, ldy, up, ldu, dp, ldd, bp, ldb, b_off, c_off, zp, ldz, _dt(u), _ptr(dt_bias, torch.float32),
+                                    _ptr(A_log, torch.float32), _ptr(D, torch.float32), ctypes.c_void_p(state.data_ptr()),
+                                    ctypes.c_longlong(state.stride(0)), _ptr(ctx.q_start, torch.int32), _ptr(ctx.q_len, torch.int32),
+                                    _ptr(ctx.seq_slot, torch.int32), ctx.num_items, inner, N, _stream()))
+
+
+def gated_delta(out: torch.Tensor, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, a: torch.Tensor, b: torch.Tensor, gate: torch.Tensor,
+                dt_bias: torch.Tensor, A_log: torch.Tensor, norm_w: torch.Tensor, eps: float, state: torch.Tensor, ctx,
+                heads: int, kv_heads: int, dim: int, vdim: int) -> None:
+  """The gated delta rule over each item's new tokens, from and to the per-request state ``[slots, >= heads * dim * vdim]``
+  float32.  ``q``, ``k`` ``[T, kv_heads * dim]`` (convolved and activated; made unit vectors here, q also times dim^-1/2),
+  ``v [T, heads * vdim]``, ``a [T, heads * dim]`` (decay input: g = exp(-exp(A_log_h) softplus(a + dt_bias))), ``b [T, heads]``
+  (beta = sigmoid(b)), ``gate [T, heads * vdim]``; per head ``S <- diag(g) S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q``;
+  ``out = o / rms(o) * norm_w * sigmoid(gate)``.  All operands may be column ranges of wider rows."""
+  lib = common_lib()
+  T = v.shape[0]
+  if (q.shape != (T, kv_heads * dim) or k.shape != q.shape or v.shape != (T, heads * vdim) or a.shape != (T, heads * dim) or b.shape != (T, heads)
+      or gate.shape != v.shape or out.shape != v.shape or dt_bias.shape != (heads * dim,) or A_log.shape != (heads,) or norm_w.shape != (vdim,)):
+    raise KernelError("gated_delta: shapes do not match")
+  if len({t.dtype for t in (out, q, k, v, a, b, gate)}) != 1:
+    raise KernelError("gated_delta: the activations differ in dtype")
+  if state.dim() != 2 or state.stride(1) != 1 or state.dtype != torch.float32:
+    raise KernelError("gated_delta: the state must be float32 rows, one per request slot")
+  (op, ldo), (qp, ldq), (kp, ldk), (vp, ldv), (ap, lda), (bp, ldb), (gp, ldg) = (_cols(t, "gated_delta") for t in (out, q, k, v, a, b, gate))
+  if ldq != ldk:
+    raise KernelError("gated_delta: q and k must be column ranges of rows of one width")
+  _check(lib, lib.mi_gated_delta(op, ldo, qp, kp, ldq, vp, ldv, ap, lda, bp, ldb, gp, ldg, _dt(v), _ptr(dt_bias, torch.float32),
+                                 _ptr(A_log, torch.float32), _ptr(norm_w, torch.float32), ctypes.c_float(eps),
+                                 ctypes.c_void_p(state.data_ptr()), ctypes.c_longlong(state.stride(0)), _ptr(ctx.q_start, torch.int32),
+                                 _ptr(ctx.q_len, torch.int32), _ptr(ctx.seq_slot, torch.int32), ctx.num_items, heads, kv_heads, dim, vdim,
+                                 _stream()))
+
+
+def latent_down(down: torch.Tensor, q_off: int, kv_off: int, q_rank: int, kv_rank: int, rot_dim: int, q_weight: torch.Tensor,
+                kv_weight: torch.Tensor, eps: float, cq_out: torch.Tensor, rope: torch.Tensor, positions: torch.Tensor, interleaved: bool,
+                slot_mapping: Optional[torch.Tensor], kv_layer: Optional[torch.Tensor]) -> None:
+  """From the fused down-projection rows of a latent attention: the RMS-normed query latent (``q_rank`` values at ``q_off``)
+  into ``cq_out [T, q_rank]``; the RMS-normed key/value latent (``kv_rank`` values at ``kv_off``) and the rotated shared key
+  part (``rot_dim`` values behind it) into the layer's pages: key row ``[c | k_rot | 0]``, value row ``[c | 0]``."""
+  lib = common_lib()
+  T = down.shape[0]
+  if max(q_off + q_rank, kv_off + kv_rank + rot_dim) > down.shape[1] or cq_out.shape != (T, q_rank) or cq_out.dtype != down.dtype:
+    raise KernelError("latent_down: the latents do not fit the projection rows")
+  if rope.shape[1] != rot_dim or q_weight.shape != (q_rank,) or kv_weight.shape != (kv_rank,):
+    raise KernelError("latent_down: weights or rotation table do not match")
+  hdp, page_size = kv_rank + rot_dim, 0
+  if kv_layer is not None:
+    if kv_layer.dtype != down.dtype or kv_layer.dim() != 5 or kv_layer.shape[1:3] != (2, 1) or kv_layer.shape[4] < kv_rank + rot_dim:
+      raise KernelError(f"latent_down: cache layer has shape {tuple(kv_layer.shape)}")
+    page_size, hdp = kv_layer.shape[3], kv_layer.shape[4]
+  none = _ptr(None)
+  _check(lib, lib.mi_latent_down(_ptr(down), _dt(down), down.shape[1], q_off, kv_off, T, q_rank, kv_rank, rot_dim, hdp,
+                                 _ptr(q_weight, torch.float32), _ptr(kv_weight, torch.float32), ctypes.c_float(eps), _ptr(cq_out),
+                                 _ptr(rope, torch.float32), _ptr(positions, torch.int32), int(bool(interleaved)),
+                                 _ptr(slot_mapping, torch.int32) if (slot_mapping is not None and kv_layer is not None) else none,
+                                 _ptr(kv_layer) if kv_layer is not None else none, page_size, _stream()))
+
+
+def latent_query(q: torch.Tensor, q_out: torch.Tensor, heads: int, dim: int, rot_dim: int, kv_rank: int, rope: torch.Tensor,
+                 positions: torch.Tensor, interleaved: bool) -> None:
+  """The rotated part of every query head (``rot_dim`` values behind the head's ``dim`` unrotated ones in ``q [T, heads * (dim +
+  rot_dim)]``), rotated, into ``q_out [T, heads * hdp]`` behind each head's first ``kv_rank`` values; the rest of a head is zeroed."""
+  lib = common_lib()
+  T = q.shape[0]
+  hdp = q_out.shape[1] // heads
+  if q.shape != (T, heads * (dim + rot_dim)) or q_out.shape != (T, heads * hdp) or hdp < kv_rank + rot_dim or q_out.dtype != q.dtype or rope.shape[1] != rot_dim:
+    raise KernelError("latent_query: shapes do not match")
+  _check(lib, lib.mi_latent_query(_ptr(q), _dt(q), q.shape[1], T, heads, dim, rot_dim, kv_rank, hdp, _ptr(q_out), _ptr(rope, torch.float32),
+                                  _ptr(positions, torch.int32), int(bool(interleaved)), _stream()))
 
 
 MOE_TC_ROW_TILE = 256            # rows of a stretch of the tcgen05 grouped product: what a pair of blocks takes at a time
@@ -599,14 +798,16 @@ class AttentionBatch:
 def attention(out: torch.Tensor, qkv: torch.Tensor, kv_layer: torch.Tensor, block_table: torch.Tensor,
               batch: AttentionBatch, num_heads: int, num_kv_heads: int, head_dim: int, scale: float,
               window: Optional[int], force_generic: bool = False, sink: Optional[torch.Tensor] = None,
-              gate: Optional[torch.Tensor] = None, gate_offset: int = 0, out_hd: Optional[int] = None) -> None:
+              gate: Optional[torch.Tensor] = None, gate_offset: int = 0, out_hd: Optional[int] = None,
+              keep_first: int = 0) -> None:
   """out[t, h*hd:(h+1)*hd] = softmax(scale * q . K^T over the keys the token may see) V, reading
   K and V through the block table.  ``qkv`` holds the step's fused rows; q is its first part.
 
   Options: ``sink [heads]`` float32 - a learned logit per query head whose exponential joins the softmax's denominator
   once, unscaled, with no key and no value; ``gate`` - rows ``[tokens, width]`` whose columns from ``gate_offset`` on hold,
   head after head, a gate for every output value: the output is multiplied with its sigmoid; ``out_hd`` - only the first
-  ``out_hd`` values of each head are written, ``out`` being ``[tokens, heads * out_hd]`` (cache rows padded to ``head_dim``)."""
+  ``out_hd`` values of each head are written, ``out`` being ``[tokens, heads * out_hd]`` (cache rows padded to ``head_dim``);
+  ``keep_first`` - with a window, every token also sees the first ``keep_first`` keys of its request."""
   T = qkv.shape[0]
   ohd = head_dim if out_hd is None else int(out_hd)
   if out.shape != (T, num_heads * ohd) or out.dtype != qkv.dtype or kv_layer.dtype != qkv.dtype or not (0 < ohd <= head_dim):
@@ -623,6 +824,7 @@ def attention(out: torch.Tensor, qkv: torch.Tensor, kv_layer: torch.Tensor, bloc
       raise KernelError("attention: the gate rows do not match")
   opts = _AttentionOptions(sink, gate, gate_offset, gate_stride, ohd)
   win = int(window) if window else 0
+  opts.keep_first = int(keep_first) if win else 0
   even = ohd % 2 == 0 and gate_offset % 2 == 0 and gate_stride % 2 == 0
   if qkv.dtype == torch.bfloat16 and not force_generic and head_dim % 16 == 0 and 16 <= head_dim <= 256 and even:
     _attention_bf16(out, qkv, kv_layer, block_table, batch, num_heads, num_kv_heads, head_dim, scale, win, page_size, opts)
@@ -632,16 +834,17 @@ def attention(out: torch.Tensor, qkv: torch.Tensor, kv_layer: torch.Tensor, bloc
     _ptr(out), _ptr(qkv), qkv.shape[1], _dt(qkv), _ptr(kv_layer), _ptr(block_table, torch.int32),
     block_table.shape[1], _ptr(batch.token_item, torch.int32), _ptr(batch.positions, torch.int32),
     _ptr(batch.seq_slot, torch.int32), T, num_heads, num_kv_heads, head_dim, page_size,
-    ctypes.c_float(scale), win, opts.sink_ptr(), opts.gate_ptr(), gate_stride, ohd, _stream()))
+    ctypes.c_float(scale), win, opts.sink_ptr(), opts.gate_ptr(), gate_stride, ohd, opts.keep_first, _stream()))
 
 
 class _AttentionOptions:
   """The optional sink, output gate and output width of an attention call, as the kernels take them."""
 
-  __slots__ = ("sink", "gate", "gate_offset", "gate_stride", "out_hd")
+  __slots__ = ("sink", "gate", "gate_offset", "gate_stride", "out_hd", "keep_first")
 
-  def __init__(self, sink, gate, gate_offset, gate_stride, out_hd):
+  def __init__(self, sink, gate, gate_offset, gate_stride, out_hd, keep_first=0):
     self.sink, self.gate, self.gate_offset, self.gate_stride, self.out_hd = sink, gate, gate_offset, gate_stride, out_hd
+    self.keep_first = keep_first
 
   def plain(self, head_dim: int) -> bool:
     return self.sink is None and self.gate is None and self.out_hd == head_dim
@@ -767,11 +970,12 @@ def _attention_bf16(out, qkv, kv_layer, block_table, batch, nh, nkv, hd, scale, 
   lib = attention_lib(hd)
   if opts is None:
     opts = _AttentionOptions(None, None, 0, 0, hd)
-  whole_heads = opts.out_hd == hd      # the TMA and tcgen05 kernels write whole heads; sink and gate they take
+  # the TMA and tcgen05 kernels write whole heads and know windows without kept first keys; sink and gate they take
+  whole_heads = opts.out_hd == hd and not opts.keep_first
   if batch.num_prefill_tiles:
     # the tcgen05 kernel takes sink and gate; its output rows are whole heads, and it reads the gate 16 bytes at a time
     gate_ok = opts.gate is None or (opts.gate_offset % 8 == 0 and opts.gate_stride % 8 == 0 and opts.gate.data_ptr() % 16 == 0)
-    use_tc = (opts.out_hd == hd and gate_ok and page_size % 64 == 0 and lib.mi_attention_prefill_tc_supported() == 1
+    use_tc = (whole_heads and gate_ok and page_size % 64 == 0 and lib.mi_attention_prefill_tc_supported() == 1
               and os.environ.get("MINIINFER_B200_PREFILL_TC", "1") != "0")
     if use_tc:
       if batch.scratch is not None:
@@ -797,7 +1001,8 @@ def _attention_bf16(out, qkv, kv_layer, block_table, batch, nh, nkv, hd, scale, 
         _ptr(out), _ptr(qkv), qkv.shape[1], _ptr(kv_layer), _ptr(block_table, torch.int32), block_table.shape[1],
         _ptr(batch.prefill_tiles, torch.int32), batch.num_prefill_tiles, _ptr(batch.q_start, torch.int32),
         _ptr(batch.q_len, torch.int32), _ptr(batch.ctx_len, torch.int32), _ptr(batch.seq_slot, torch.int32),
-        nh, nkv, page_size, ctypes.c_float(scale), win, opts.sink_ptr(), opts.gate_ptr(), opts.gate_stride, opts.out_hd, _stream()))
+        nh, nkv, page_size, ctypes.c_float(scale), win, opts.sink_ptr(), opts.gate_ptr(), opts.gate_stride, opts.out_hd,
+        opts.keep_first, _stream()))
   if batch.num_decode:
     span = min(batch.max_ctx_len, win) if win else batch.max_ctx_len
     G = nh // nkv
@@ -826,7 +1031,7 @@ def _attention_bf16(out, qkv, kv_layer, block_table, batch, nh, nkv, hd, scale, 
       max_splits = min(-(-span // 64) + 2, _num_sms(qkv.device))
     else:
       chunk = batch.decode_chunk or decode_chunk(batch.num_decode, nkv, span, hd)
-      max_splits = -(-span // chunk) + 1
+      max_splits = -(-span // chunk) + 1 + -(-opts.keep_first // chunk)
     n = batch.num_decode * nh * max_splits * (hd + 2)
     if batch.scratch is not None:
       scratch = batch.scratch.buffer("attention_decode_partials", (n,), torch.float32)
@@ -849,7 +1054,7 @@ def _attention_bf16(out, qkv, kv_layer, block_table, batch, nh, nkv, hd, scale, 
         _ptr(batch.decode_items, torch.int32), _ptr(batch.q_start, torch.int32), _ptr(batch.ctx_len, torch.int32),
         _ptr(batch.seq_slot, torch.int32), _ptr(scratch, torch.float32), _ptr(counters[1:], torch.int32),
         batch.num_decode, nh, nkv, page_size, ctypes.c_float(scale), win, chunk, max_splits,
-        opts.sink_ptr(), opts.gate_ptr(), opts.gate_stride, opts.out_hd, _stream()))
+        opts.sink_ptr(), opts.gate_ptr(), opts.gate_stride, opts.out_hd, opts.keep_first, _stream()))
 
 
 _tensor_maps: Dict[tuple, ctypes.Array] = {}

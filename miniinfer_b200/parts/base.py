@@ -154,6 +154,11 @@ class Norm(Part):
   def add_norm(self, resid: torch.Tensor, delta: Optional[torch.Tensor], ctx) -> torch.Tensor:
     raise NotImplementedError
 
+  def add_norm_pair(self, resid: torch.Tensor, delta, other: "Norm", ctx):
+    """``add_norm`` and, of the same summed rows, ``other``'s norm: (rows by this norm, rows by ``other``).  For blocks
+    whose mixer and feed-forward have a norm each; a kind of norm that cannot share the pass says so."""
+    raise NotImplementedError(f"{type(self).__name__} does not pair with another norm")
+
   def norm_rows(self, resid: torch.Tensor, delta: Optional[torch.Tensor], rows: torch.Tensor, ctx) -> torch.Tensor:
     raise NotImplementedError
 
@@ -174,6 +179,8 @@ class PositionEncoding(Part):
 
 
 class Mixer(Part):
+  out_buffer = "mixer_out"      # the workspace buffer of the mixer's output; a mixer made of mixers gives each member its own
+
   def cache_spec(self) -> Optional[CacheSpec]:
     return None
 

@@ -46,25 +46,30 @@ class PreNormBlock(Block):
 
 
 class ParallelBlock(Block):
-  """One norm a layer; mixer and feed-forward both read its output: with ``h = norm(x)``, ``x <- x + (mixer(h) + ff(h))``.
-  The two outputs are left pending as a pair and added, in float32, by the norm that comes next.  ``ffn`` may be None
-  (a layer without a feed-forward)."""
+  """Mixer and feed-forward side by side on the same residual rows: ``x <- x + (mixer(norm(x)) + ff(ffn_norm(x)))``.
+  With one norm (``ffn_norm`` None) both read its output; with two, each has a norm of its own on the same rows, and the
+  two are computed together (``Norm.add_norm_pair``: one root mean square, two weights).  The two outputs are left pending
+  as a pair and added, in float32, by the norm that comes next.  ``ffn`` may be None (a layer without a feed-forward)."""
 
-  def __init__(self, name: str, norm: Norm, mixer: Mixer, ffn: Optional[FeedForward]):
+  def __init__(self, name: str, norm: Norm, mixer: Mixer, ffn: Optional[FeedForward], ffn_norm: Optional[Norm] = None):
     super().__init__(name)
     self.norm = norm
     self.mixer = mixer
     self.ffn = ffn
+    self.ffn_norm = ffn_norm if ffn is not None else None
 
   def sub_parts(self) -> List[Part]:
-    return [self.norm, self.mixer] + ([self.ffn] if self.ffn is not None else [])
+    return [self.norm, self.mixer] + ([self.ffn_norm] if self.ffn_norm is not None else []) + ([self.ffn] if self.ffn is not None else [])
 
   def mixer_part(self) -> Optional[Mixer]:
     return self.mixer
 
   def forward(self, resid: torch.Tensor, pending, ctx, cache):
-    x = self.norm.add_norm(resid, pending, ctx)
+    if self.ffn_norm is not None:
+      x, x_ffn = self.norm.add_norm_pair(resid, pending, self.ffn_norm, ctx)
+    else:
+      x = x_ffn = self.norm.add_norm(resid, pending, ctx)
     a = self.mixer.forward(x, ctx, cache)
     if self.ffn is None:
       return a
-    return (a, self.ffn.forward(x, ctx))
+    return (a, self.ffn.forward(x_ffn, ctx))

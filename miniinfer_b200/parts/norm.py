@@ -30,31 +30,56 @@ def split_delta(delta: Delta) -> Tuple[Optional[torch.Tensor], Optional[torch.Te
 
 
 class RMSNorm(Norm):
-  def __init__(self, name: str, dim: int, eps: float):
+  """``(offset + w) * x / sqrt(mean(x^2) + eps)`` in float32, the residual add (of one or two pending outputs) in front
+  of it in the same kernel.  ``offset``: 0 for a weight stored as it is applied, 1 for a weight stored around zero (the
+  sum is made once, in float32, when the weights are bound).  ``weight_name``: the file tensor (default ``<name>.weight``)."""
+
+  def __init__(self, name: str, dim: int, eps: float, offset: float = 0.0, weight_name: Optional[str] = None):
     super().__init__(name)
     self.dim = dim
     self.eps = float(eps)
+    self.offset = float(offset)
+    self.weight_name = weight_name or f"{name}.weight"
 
   def param_specs(self) -> Dict[str, ParamSpec]:
-    return {"weight": ParamSpec((self.dim,), "vector", [whole(f"{self.name}.weight", (self.dim,))], init="ones_noise")}
+    return {"weight": ParamSpec((self.dim,), "vector", [whole(self.weight_name, (self.dim,))],
+                                init="ones_noise" if self.offset == 0.0 else "normal")}
+
+  def bind(self, params) -> None:
+    super().bind(params)
+    if self.offset != 0.0 and "weight" in params:
+      self.weight = params["weight"] + self.offset          # the stored tensor stays as the file has it
 
   def as_rms(self):
     return self.weight, self.eps
 
   def add_norm(self, resid: torch.Tensor, delta: Delta, ctx) -> torch.Tensor:
     first, second = split_delta(delta)
-    if second is not None:
-      raise NotImplementedError("RMSNorm adds one pending output; put a LayerNorm behind a block that leaves two")
     out = ctx.ws.buffer("normed", (resid.shape[0], self.dim), ctx.dtype)
-    ops.add_rmsnorm(out, resid, first, self.weight, self.eps, None, True)
+    if second is not None:
+      ops.add_rmsnorm_pair(out, None, resid, first, second, self.weight, None, self.eps, None, True)
+    else:
+      ops.add_rmsnorm(out, resid, first, self.weight, self.eps, None, True)
     return out
+
+  def add_norm_pair(self, resid: torch.Tensor, delta: Delta, other: "RMSNorm", ctx) -> Tuple[torch.Tensor, torch.Tensor]:
+    """What ``add_norm`` does, and the rows normalised with ``other``'s weight as well: two norms of the same rows share
+    the root mean square (``other`` must be an RMSNorm of the same size and eps)."""
+    if not isinstance(other, RMSNorm) or other.dim != self.dim or other.eps != self.eps:
+      raise ValueError(f"{self.name}: a pair of norms must be two RMS norms of one size and eps")
+    first, second = split_delta(delta)
+    out = ctx.ws.buffer("normed", (resid.shape[0], self.dim), ctx.dtype)
+    out2 = ctx.ws.buffer("normed_second", (resid.shape[0], self.dim), ctx.dtype)
+    ops.add_rmsnorm_pair(out, out2, resid, first, second, self.weight, other.weight, self.eps, None, True)
+    return out, out2
 
   def norm_rows(self, resid: torch.Tensor, delta: Delta, rows: torch.Tensor, ctx) -> torch.Tensor:
     first, second = split_delta(delta)
-    if second is not None:
-      raise NotImplementedError("RMSNorm adds one pending output; put a LayerNorm behind a block that leaves two")
     out = ctx.ws.buffer("normed_rows", (rows.shape[0], self.dim), ctx.dtype)
-    ops.add_rmsnorm(out, resid, first, self.weight, self.eps, rows, False)
+    if second is not None:
+      ops.add_rmsnorm_pair(out, None, resid, first, second, self.weight, None, self.eps, rows, False)
+    else:
+      ops.add_rmsnorm(out, resid, first, self.weight, self.eps, rows, False)
     return out
 
 

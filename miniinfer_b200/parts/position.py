@@ -42,3 +42,44 @@ class RotaryEncoding(PositionEncoding):
 
   def max_positions(self) -> Optional[int]:
     return self.max_position_embeddings
+
+
+class ScaledRotaryEncoding(RotaryEncoding):
+  """Rotary angles whose frequencies are stretched for contexts longer than the ``original`` one (YaRN): with
+  ``f_i = theta^(-2i/dims)`` and ``turns(t) = dims * ln(original / (2 pi t)) / (2 ln theta)`` - the index of the frequency
+  that makes ``t`` turns over the original context - frequencies below index ``lo = max(floor(turns(fast)), 0)`` stay,
+  those above ``hi = min(ceil(turns(slow)), dims - 1)`` are divided by ``factor``, those between are blended linearly
+  (``ramp_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1)``, ``f_i <- f_i / factor * ramp_i + f_i * (1 - ramp_i)``), and cos
+  and sin are multiplied by ``0.1 ln(factor) + 1``.  Angles are made in float64 and rounded once.  Without ``scaling``
+  this is the plain table."""
+
+  def __init__(self, name: str, rotary_dim: int, theta: float, max_position_embeddings: int, scaling: Optional[dict] = None):
+    super().__init__(name, rotary_dim, theta, max_position_embeddings)
+    if scaling is not None:
+      for key in ("factor", "original", "fast", "slow"):
+        if not isinstance(scaling.get(key), (int, float)) or not scaling[key] > 0:
+          raise ValueError(f"{name}: scaling.{key} must be a positive number, got {scaling.get(key)!r}")
+    self.scaling = dict(scaling) if scaling is not None else None
+
+  def frequencies(self):
+    """(frequencies [dims / 2] in float64, the factor on cos and sin)."""
+    import math
+    dims = self.rotary_dim
+    i = torch.arange(0, dims // 2, dtype=torch.float64)
+    f = self.theta ** (-2.0 * i / dims)
+    s = self.scaling
+    if s is None:
+      return f, 1.0
+
+    def turns(t):
+      return dims * math.log(s["original"] / (2 * math.pi * t)) / (2 * math.log(self.theta))
+
+    lo = max(math.floor(turns(s["fast"])), 0)
+    hi = min(math.ceil(turns(s["slow"])), dims - 1)
+    ramp = ((i - lo) / max(hi - lo, 0.001)).clamp(0.0, 1.0)
+    return f / s["factor"] * ramp + f * (1.0 - ramp), 0.1 * math.log(s["factor"]) + 1.0
+
+  def build_table(self, positions: int) -> torch.Tensor:
+    f, m = self.frequencies()
+    angles = torch.arange(positions, dtype=torch.float64)[:, None] * f[None, :]
+    return torch.cat((angles.cos() * m, angles.sin() * m), dim=-1).float().contiguous()

@@ -63,6 +63,14 @@ def _index_files(model_dir: str) -> Dict[str, Tuple[str, Tuple[int, ...]]]:
   return index
 
 
+def tensor_shapes(model_dir: str) -> Dict[str, Tuple[int, ...]]:
+  """Name -> shape of every tensor of the folder's weights files, from their headers; empty if there are none."""
+  try:
+    return {name: shape for name, (_, shape) in _index_files(model_dir).items()}
+  except FileNotFoundError:
+    return {}
+
+
 def load_weights(spec: ModelSpec, model_dir: str, compute_dtype: torch.dtype, device) -> None:
   """Fills and binds the parameters of every part of ``spec``."""
   from safetensors import safe_open

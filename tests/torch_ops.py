@@ -109,7 +109,8 @@ def qk_norm_rope_store(qkv, q_weight, k_weight, cos_sin, positions, slot_mapping
 
 
 def qkv_norm_mix_store(proj, q_off, k_off, v_off, q_out, num_heads, num_kv_heads, dim, vdim, eps, normalise=True,
-                       q_weight=None, k_weight=None, mix=None, v_other=None, v_mode=0, slot_mapping=None, kv_layer=None):
+                       q_weight=None, k_weight=None, mix=None, v_other=None, v_mode=0, slot_mapping=None, kv_layer=None,
+                       rope=None, positions=None, interleaved=False):
   T = proj.shape[0]
   H, G = num_heads, num_kv_heads
   hdp = q_out.shape[1] // H
@@ -124,6 +125,8 @@ def qkv_norm_mix_store(proj, q_off, k_off, v_off, q_out, num_heads, num_kv_heads
     q = q * q_weight
   if k_weight is not None:
     k = k * k_weight
+  if rope is not None:
+    q, k = _rotate(q, rope, positions, interleaved), _rotate(k, rope, positions, interleaved)
   if v_mode == 1:
     v_other.copy_(v.reshape(T, G * vdim).to(v_other.dtype))
   elif v_mode == 2:
@@ -142,6 +145,21 @@ def qkv_norm_mix_store(proj, q_off, k_off, v_off, q_out, num_heads, num_kv_heads
     vp[..., :vdim] = v
     kv_layer[page, 0, :, off, :] = kp.to(kv_layer.dtype)
     kv_layer[page, 1, :, off, :] = vp.to(kv_layer.dtype)
+
+
+def _rotate(t, table, positions, interleaved):
+  """t [T, heads, size]: the first table.shape[1] values of every head rotated by the angles of the token's position."""
+  rot = table.shape[1]
+  cs = table[positions.long()]
+  c, s = cs[:, None, :rot // 2], cs[:, None, rot // 2:]
+  out = t.clone()
+  if interleaved:
+    u, v = t[..., 0:rot:2], t[..., 1:rot:2]
+    out[..., 0:rot:2], out[..., 1:rot:2] = u * c - v * s, v * c + u * s
+  else:
+    u, v = t[..., :rot // 2], t[..., rot // 2:rot]
+    out[..., :rot // 2], out[..., rot // 2:rot] = u * c - v * s, v * c + u * s
+  return out
 
 
 def routed_experts(out, x, router, correction, gate_up, down, top, workspace):
@@ -163,10 +181,10 @@ def routed_experts(out, x, router, correction, gate_up, down, top, workspace):
 
 
 def attention(out, qkv, kv_layer, block_table, batch, num_heads, num_kv_heads, head_dim, scale, window,
-              force_generic=False, sink=None, gate=None, gate_offset=0, out_hd=None):
-  if sink is not None or gate is not None or (out_hd is not None and out_hd != head_dim):
+              force_generic=False, sink=None, gate=None, gate_offset=0, out_hd=None, keep_first=0):
+  if sink is not None or gate is not None or (out_hd is not None and out_hd != head_dim) or keep_first:
     return _attention_with_options(out, qkv, kv_layer, block_table, batch, num_heads, num_kv_heads, head_dim, scale,
-                                   window, sink, gate, gate_offset, out_hd if out_hd is not None else head_dim)
+                                   window, sink, gate, gate_offset, out_hd if out_hd is not None else head_dim, keep_first)
   T = qkv.shape[0]
   nh, nkv, hd = num_heads, num_kv_heads, head_dim
   P = kv_layer.shape[3]
@@ -191,7 +209,8 @@ def attention(out, qkv, kv_layer, block_table, batch, num_heads, num_kv_heads, h
   out.copy_(res.reshape(T, nh * hd).to(out.dtype))
 
 
-def _attention_with_options(out, qkv, kv_layer, block_table, batch, nh, nkv, hd, scale, window, sink, gate, gate_offset, ohd):
+def _attention_with_options(out, qkv, kv_layer, block_table, batch, nh, nkv, hd, scale, window, sink, gate, gate_offset, ohd,
+                            keep_first=0):
   T = qkv.shape[0]
   P = kv_layer.shape[3]
   g = nh // nkv
@@ -202,6 +221,8 @@ def _attention_with_options(out, qkv, kv_layer, block_table, batch, nh, nkv, hd,
     p = pos[t]
     lo = max(0, p - window + 1) if window else 0
     js = torch.arange(lo, p + 1, device=qkv.device)
+    if window and keep_first:
+      js = torch.cat((torch.arange(0, min(keep_first, lo), device=qkv.device), js))
     pages = block_table[slots[item[t]]].long()[js // P]
     k = kv_layer[pages, 0, :, js % P, :].float().repeat_interleave(g, dim=1)
     v = kv_layer[pages, 1, :, js % P, :].float().repeat_interleave(g, dim=1)
@@ -214,6 +235,127 @@ def _attention_with_options(out, qkv, kv_layer, block_table, batch, nh, nkv, hd,
   if gate is not None:
     res = res * torch.sigmoid(gate.float()[:, gate_offset:gate_offset + nh * ohd])
   out.copy_(res.to(out.dtype))
+
+
+def add_rmsnorm_pair(out1, out2, resid, delta, delta2, w1, w2, eps, rows=None, write_back=True):
+  idx = rows.long() if rows is not None else None
+  x = resid if idx is None else resid[idx]
+  ds = [d for d in (delta, delta2) if d is not None]
+  if ds:
+    add = ds[0].float() if len(ds) == 1 else ds[0].float() + ds[1].float()
+    x = x + (add if idx is None else add[idx])
+    if write_back:
+      if idx is None:
+        resid.copy_(x)
+      else:
+        resid[idx] = x
+  n = x / torch.sqrt(x.pow(2).mean(-1, keepdim=True) + eps)
+  out1.copy_((w1 * n).to(out1.dtype))
+  if out2 is not None:
+    out2.copy_((w2 * n).to(out2.dtype))
+
+
+def rms_pair_sum(out, a, b, w1, w2, eps, scale):
+  def unit(t):
+    t = t.float()
+    return t / torch.sqrt(t.pow(2).mean(-1, keepdim=True) + eps)
+  out.copy_((scale * (w1 * unit(a) + w2 * unit(b))).to(out.dtype))
+
+
+def linear_batched(out, x, w, bias=None, softplus=False, row_gate=None):
+  y = torch.einsum("mbk,bnk->mbn", x.float(), w.float())
+  if bias is not None:
+    y = y + bias
+  if softplus:
+    y = torch.nn.functional.softplus(y)
+  if row_gate is not None:
+    y = y * torch.sigmoid(row_gate.float()[:, :x.shape[1], None])
+  out.copy_(y.to(out.dtype))
+
+
+def _items(ctx):
+  return list(zip(ctx.q_start.tolist(), ctx.q_len.tolist(), ctx.seq_slot.tolist()))
+
+
+def causal_conv(out, x, weight, bias, state, ctx, silu=True):
+  C, taps = weight.shape
+  S = taps - 1
+  for row0, n, slot in _items(ctx):
+    old = state[slot, :S * C].view(S, C) if S else x.new_zeros((0, C), dtype=torch.float32)
+    seq = torch.cat((old.float(), x[row0:row0 + n].float()), dim=0)
+    y = sum(seq[k:k + n] * weight[:, k] for k in range(taps))
+    if bias is not None:
+      y = y + bias
+    if silu:
+      y = y * torch.sigmoid(y)
+    out[row0:row0 + n] = y.to(out.dtype)
+    if S:
+      state[slot, :S * C] = seq[seq.shape[0] - S:].reshape(-1)
+
+
+def selective_scan(y, u, dt_in, bc, b_off, c_off, z, dt_bias, A_log, D, state, ctx):
+  inner, N = A_log.shape
+  A = -torch.exp(A_log.float())
+  for row0, n, slot in _items(ctx):
+    S = state[slot, :inner * N].view(inner, N).clone()
+    for t in range(row0, row0 + n):
+      dt = torch.nn.functional.softplus(dt_in[t].float() + dt_bias)
+      ut = u[t].float()
+      S = torch.exp(dt[:, None] * A) * S + (dt * ut)[:, None] * bc[t, b_off:b_off + N].float()[None, :]
+      zt = z[t].float()
+      y[t] = ((S @ bc[t, c_off:c_off + N].float() + D * ut) * (zt * torch.sigmoid(zt))).to(y.dtype)
+    state[slot, :inner * N] = S.reshape(-1)
+
+
+def gated_delta(out, q, k, v, a, b, gate, dt_bias, A_log, norm_w, eps, state, ctx, heads, kv_heads, dim, vdim):
+  H, G, D, Dv = heads, kv_heads, dim, vdim
+  for row0, n, slot in _items(ctx):
+    S = state[slot, :H * D * Dv].view(H, D, Dv).clone()
+    for t in range(row0, row0 + n):
+      qt, kt = q[t].float().view(G, D), k[t].float().view(G, D)
+      qt = qt / torch.sqrt(qt.pow(2).sum(-1, keepdim=True) + 1e-6) * D ** -0.5
+      kt = kt / torch.sqrt(kt.pow(2).sum(-1, keepdim=True) + 1e-6)
+      qt, kt = qt.repeat_interleave(H // G, dim=0), kt.repeat_interleave(H // G, dim=0)        # [H, D]
+      g = torch.exp(-torch.exp(A_log.float())[:, None] * torch.nn.functional.softplus(a[t].float().view(H, D) + dt_bias.view(H, D)))
+      beta = torch.sigmoid(b[t].float())                                                       # [H]
+      S = g[:, :, None] * S
+      u = beta[:, None] * (v[t].float().view(H, Dv) - torch.einsum("hdv,hd->hv", S, kt))
+      S = S + kt[:, :, None] * u[:, None, :]
+      o = torch.einsum("hdv,hd->hv", S, qt)
+      o = o / torch.sqrt(o.pow(2).mean(-1, keepdim=True) + eps) * norm_w * torch.sigmoid(gate[t].float().view(H, Dv))
+      out[t] = o.reshape(-1).to(out.dtype)
+    state[slot, :H * D * Dv] = S.reshape(-1)
+
+
+def latent_down(down, q_off, kv_off, q_rank, kv_rank, rot_dim, q_weight, kv_weight, eps, cq_out, rope, positions, interleaved,
+                slot_mapping, kv_layer):
+  T = down.shape[0]
+  x = down.float()
+
+  def unit(t):
+    return t / torch.sqrt(t.pow(2).mean(-1, keepdim=True) + eps)
+
+  cq_out.copy_((q_weight * unit(x[:, q_off:q_off + q_rank])).to(cq_out.dtype))
+  if slot_mapping is None or kv_layer is None:
+    return
+  c = kv_weight * unit(x[:, kv_off:kv_off + kv_rank])
+  kr = _rotate(x[:, None, kv_off + kv_rank:kv_off + kv_rank + rot_dim], rope, positions, interleaved)[:, 0]
+  P, hdp = kv_layer.shape[3], kv_layer.shape[4]
+  krow = torch.zeros((T, hdp), dtype=torch.float32, device=down.device)
+  vrow = torch.zeros((T, hdp), dtype=torch.float32, device=down.device)
+  krow[:, :kv_rank], krow[:, kv_rank:kv_rank + rot_dim], vrow[:, :kv_rank] = c, kr, c
+  slot = slot_mapping.long()
+  kv_layer[slot // P, 0, 0, slot % P, :] = krow.to(kv_layer.dtype)
+  kv_layer[slot // P, 1, 0, slot % P, :] = vrow.to(kv_layer.dtype)
+
+
+def latent_query(q, q_out, heads, dim, rot_dim, kv_rank, rope, positions, interleaved):
+  T = q.shape[0]
+  hdp = q_out.shape[1] // heads
+  qr = _rotate(q.float().view(T, heads, dim + rot_dim)[:, :, dim:], rope, positions, interleaved)
+  dst = q_out.view(T, heads, hdp)
+  dst[:, :, kv_rank:kv_rank + rot_dim] = qr.to(q_out.dtype)
+  dst[:, :, kv_rank + rot_dim:] = 0
 
 
 def linear_swiglu(out, x, w, workspace, force_skinny=False, force_tc=False):
@@ -276,5 +418,7 @@ def install(monkeypatch) -> None:
   from miniinfer_b200.kernels import ops
 
   for name in ("embedding", "add_rmsnorm", "add_layernorm", "linear", "linear_swiglu", "qk_norm_rope_store", "qkv_norm_mix_store",
-               "attention", "routed_experts", "silu_mul", "sample", "linear_normed", "linear_swiglu_normed", "linear_add"):
+               "attention", "routed_experts", "silu_mul", "sample", "linear_normed", "linear_swiglu_normed", "linear_add",
+               "add_rmsnorm_pair", "rms_pair_sum", "linear_batched", "causal_conv", "selective_scan", "gated_delta", "latent_down",
+               "latent_query"):
     monkeypatch.setattr(ops, name, globals()[name])
