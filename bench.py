@@ -800,8 +800,189 @@ def compare_one(name: str, cfg: dict, size: dict, batch: int, steps: int, warmup
   return out
 
 
+# ---------------------------------------------------------------------------------------------- --compare vugudra
+# Sizes for the comparison of the Vugudra design with the Qwen3 dense decoder at equal size: width, dense feed-forward,
+# layers, and the sizes of the three mixers at about the weights of the dense decoder's attention.  The layers go
+# selective scan, latent attention, windowed attention beside a gated delta rule, and again; the Qwen3 model has the heads
+# of the windowed attention, its window and the same vocabulary.
+VUGUDRA_SIZES = {
+  "s": dict(width=1024, ff=3072, layers=6, heads=16, kv_heads=8, head=128,
+            scan=dict(inner=2048, state=16, dt_rank=64, conv=4),
+            latent=dict(heads=16, dim=64, rot_dim=32, vdim=64, kv_rank=192, q_rank=384),
+            delta=dict(heads=8, kv_heads=4, dim=128, vdim=128, conv=4, rank=64)),
+  "m": dict(width=2048, ff=6144, layers=6, heads=32, kv_heads=8, head=64,
+            scan=dict(inner=4096, state=16, dt_rank=128, conv=4),
+            latent=dict(heads=32, dim=64, rot_dim=64, vdim=64, kv_rank=192, q_rank=768),
+            delta=dict(heads=16, kv_heads=8, dim=128, vdim=128, conv=4, rank=128)),
+  "l": dict(width=4096, ff=12288, layers=3, heads=32, kv_heads=8, head=128,
+            scan=dict(inner=8192, state=16, dt_rank=256, conv=4),
+            latent=dict(heads=32, dim=128, rot_dim=64, vdim=128, kv_rank=192, q_rank=1536),
+            delta=dict(heads=32, kv_heads=16, dim=128, vdim=128, conv=4, rank=128)),
+}
+VUGUDRA_KEEP_FIRST = 4
+
+
+def vugudra_configs(size: dict) -> dict:
+  W, H, G, hd, L = size["width"], size["heads"], size["kv_heads"], size["head"], size["layers"]
+  qwen = dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", num_hidden_layers=L, hidden_size=W,
+              num_attention_heads=H, num_key_value_heads=G, head_dim=hd, intermediate_size=size["ff"], vocab_size=COMPARE_VOCAB,
+              rope_theta=1000000.0, rms_norm_eps=1e-6, max_position_embeddings=40960, tie_word_embeddings=False,
+              use_sliding_window=True, sliding_window=COMPARE_WINDOW, max_window_layers=0)
+  mlp = {"kind": "dense", "ff": size["ff"]}
+  lat, dl = size["latent"], size["delta"]
+  kinds = [
+    {"type": "mamba1", "mixer": dict(size["scan"]), "mlp": mlp},
+    {"type": "latent_attention", "mlp": mlp,
+     "mixer": dict({k: lat[k] for k in ("heads", "dim", "rot_dim", "vdim", "kv_rank", "q_rank")}, scale=(lat["dim"] + lat["rot_dim"]) ** -0.5,
+                   rot={"dims": lat["rot_dim"], "base": 10000.0, "scaling": {"factor": 4.0, "original": 4096, "fast": 32.0, "slow": 1.0}})},
+    {"type": "parallel", "mlp": mlp,
+     "mixer": {"left": {"heads": H, "kv_heads": G, "dim": hd, "vdim": hd, "scale": hd ** -0.5, "rot": {"dims": hd, "base": 1000000.0},
+                        "mask": {"size": COMPARE_WINDOW, "keep_first": VUGUDRA_KEEP_FIRST}},
+               "right": {k: dl[k] for k in ("heads", "kv_heads", "dim", "vdim", "conv")}}},
+  ]
+  layers = [kinds[i % 3] for i in range(L)]
+  ranks = {f"l{i}.{w}": dl["rank"] for i in range(L) if i % 3 == 2 for w in ("decay", "gate")}
+  vug = {"architecture": "Vugudra", "vocab": COMPARE_VOCAB, "width": W, "norm": {"eps": 1e-6}, "layers": layers, "low_ranks": ranks}
+  return {"qwen3": qwen, "vugudra": vug}
+
+
+def _vugudra_groups(times: dict) -> dict:
+  import re
+  g = {"attention": 0.0, "dense_products": 0.0, "head_products": 0.0, "scan": 0.0, "delta_rule": 0.0, "convolution": 0.0, "other": 0.0}
+  for name, us in times.items():
+    if re.search(r"decode_tma_kernel|decode_cluster_kernel|decode_split_kernel|decode_merge|attention_prefill|attention_generic", name):
+      g["attention"] += us
+    elif "gemm_batched" in name:
+      g["head_products"] += us
+    elif "selective_scan" in name:
+      g["scan"] += us
+    elif "gated_delta" in name:
+      g["delta_rule"] += us
+    elif "causal_conv" in name or "conv_state" in name:
+      g["convolution"] += us
+    elif "gemm_skinny" in name or "gemm_tc_kernel" in name or "gemm_stream_tc" in name or \
+        ("anonymous namespace" not in name and re.search(r"nvjet|cutlass|cublas|gemm|gemv|xmma", name, re.I)):
+      g["dense_products"] += us
+    elif not name.startswith("Memcpy") and not name.startswith("Memset"):
+      g["other"] += us
+  return g
+
+
+def vugudra_one(name: str, cfg: dict, size: dict, batch: int, steps: int, warmup: int, pk: dict, kernels: bool) -> dict:
+  """Prefill and decode of one model of the comparison; with ``kernels`` the device time of its kinds of kernels and the
+  rates they reach against the measured peaks (run with dependent launch off, see main)."""
+  import torch
+  from miniinfer_b200.engine import StepItem
+  from miniinfer_b200.sampling import Sampler, SamplingParams
+  W, H, G, hd, L = size["width"], size["heads"], size["kv_heads"], size["head"], size["layers"]
+  win, T = COMPARE_WINDOW, PREFILL_TOKENS
+  with tempfile.TemporaryDirectory() as d:
+    with open(os.path.join(d, "config.json"), "w") as f:
+      json.dump(cfg, f)
+    engine = build_engine(d, batch)
+    if not kernels:
+      dec = time_decode(engine, batch, steps, warmup)
+      pre = time_prefill(engine)
+      out = {"decode_tok_s": round(dec["tok_s"], 1), "decode_ms": round(dec["ms"], 4), "launches_per_decode_step": int(dec["launches_per_step"]),
+             "prefill_tok_s": round(T / (pre["ms"] * 1e-3), 1), "prefill_ms": round(pre["ms"], 3)}
+    else:
+      rids = fill_context(engine, batch, CONTEXT, seed=1000 + batch)
+      params = [SamplingParams(temperature=0.6, max_tokens=GENERATED, ignore_eos=True)] * batch
+      tokens_dev = torch.zeros(max(batch, 1), dtype=torch.int32, device="cuda:0")
+
+      def decode(i):
+        extras = Sampler.pack(params, list(range(batch)), [i] * batch)
+        engine.runner.step_and_sample([StepItem(r, [1], (0,)) for r in rids], extras, Sampler.sample, tokens_dev,
+                                      sampling_pad=Sampler.PAD_ROWS)
+
+      for i in range(4):
+        decode(i)
+      torch.cuda.synchronize()
+      dk = _vugudra_groups(_kernel_times(lambda i: decode(10 + i), 4))
+      for r in rids:
+        engine.cache.release_request(r)
+      g = torch.Generator().manual_seed(7)
+
+      def whole(i):
+        rid = f"rates{i}"
+        engine.cache.admit(rid)
+        engine.runner.step([StepItem(rid, torch.randint(0, COMPARE_VOCAB, (T,), generator=g).tolist(), (T - 1,))])
+        engine.cache.release_request(rid)
+
+      for i in range(2):
+        whole(i)
+      torch.cuda.synchronize()
+      pt = _vugudra_groups(_kernel_times(lambda i: whole(10 + i), 2))
+      for grp in (pt, dk):
+        for key in grp:
+          grp[key] = max(grp[key], 1e-9)
+      ff_w = L * 3 * size["ff"] * W
+      if name == "qwen3":
+        seen = sum(min(t + 1, win) for t in range(T))
+        attn_flops = L * 4.0 * H * hd * seen
+        attn_bytes = batch * min(CONTEXT, win) * L * 2 * G * hd * 2
+        proj_w = L * ((H + 2 * G) * hd * W + W * H * hd)
+        extra = {}
+      else:
+        sc, lat, dl = size["scan"], size["latent"], size["delta"]
+        n_scan, n_lat, n_side = (L + 2) // 3, (L + 1) // 3, L // 3
+        lat_hd = lat["kv_rank"] + lat["rot_dim"]
+        seen_win = sum(min(t + 1, win + VUGUDRA_KEEP_FIRST) for t in range(T))
+        seen_all = sum(t + 1 for t in range(T))
+        # scores over the keys a token sees, and the weighted values: latent heads read kv_rank + rot_dim and give kv_rank
+        attn_flops = n_side * 4.0 * H * hd * seen_win + n_lat * 2.0 * lat["heads"] * (lat_hd + lat["kv_rank"]) * seen_all
+        lat_row = -(-lat_hd // 16) * 16
+        attn_bytes = batch * 2 * (n_side * min(CONTEXT, win + VUGUDRA_KEEP_FIRST) * 2 * G * hd + n_lat * CONTEXT * 2 * lat_row)
+        I, N, R = sc["inner"], sc["state"], sc["dt_rank"]
+        scan_w = 2 * I * W + (R + 2 * N) * I + I * R + W * I
+        lat_w = (lat["q_rank"] + lat["kv_rank"] + lat["rot_dim"] + lat["heads"]) * W + lat["heads"] * (lat["dim"] + lat["rot_dim"]) * lat["q_rank"] + W * lat["heads"] * lat["vdim"]
+        left_w = (H + G) * hd * W + W * H * hd
+        dh, dg, dd, dv, rk = dl["heads"], dl["kv_heads"], dl["dim"], dl["vdim"], dl["rank"]
+        right_w = (2 * dg * dd + dh * dv + dh + 2 * rk) * W + rk * (dh * dd + dh * dv) + W * dh * dv
+        proj_w = n_scan * scan_w + n_lat * lat_w + n_side * (left_w + right_w)
+        head_w = n_lat * lat["heads"] * lat["kv_rank"] * (lat["dim"] + lat["vdim"])
+        # what the recurrences must move: their inputs and outputs once (2 bytes a value) and, in a decode step, every
+        # request's state in and out (4 bytes a value)
+        scan_io = n_scan * (4 * I + 2 * N) * 2
+        scan_state = n_scan * I * N * 4 * 2
+        delta_io = n_side * (2 * dg * dd + dh * (3 * dv + dd + 1)) * 2
+        delta_state = n_side * dh * dd * dv * 4 * 2
+        extra = {
+          "prefill_head_products": {"us": round(pt["head_products"], 1), "TFLOP/s": round(2.0 * T * head_w / pt["head_products"] / 1e6, 1),
+                                    "frac": round(2.0 * T * head_w / pt["head_products"] / 1e6 / pk["bf16_tflops"], 4)},
+          "decode_head_products": {"us": round(dk["head_products"], 1), "GB/s": round(2.0 * head_w / dk["head_products"] / 1e3, 1),
+                                   "frac": round(2.0 * head_w / dk["head_products"] / 1e3 / pk["hbm_gbs"], 4)},
+          "prefill_scan": {"us": round(pt["scan"], 1), "GB/s": round(T * scan_io / pt["scan"] / 1e3, 1),
+                           "frac": round(T * scan_io / pt["scan"] / 1e3 / pk["hbm_gbs"], 4)},
+          "decode_scan": {"us": round(dk["scan"], 1), "GB/s": round(batch * (scan_io + scan_state) / dk["scan"] / 1e3, 1),
+                          "frac": round(batch * (scan_io + scan_state) / dk["scan"] / 1e3 / pk["hbm_gbs"], 4)},
+          "prefill_delta_rule": {"us": round(pt["delta_rule"], 1), "GB/s": round(T * delta_io / pt["delta_rule"] / 1e3, 1),
+                                 "frac": round(T * delta_io / pt["delta_rule"] / 1e3 / pk["hbm_gbs"], 4)},
+          "decode_delta_rule": {"us": round(dk["delta_rule"], 1), "GB/s": round(batch * (delta_io + delta_state) / dk["delta_rule"] / 1e3, 1),
+                                "frac": round(batch * (delta_io + delta_state) / dk["delta_rule"] / 1e3 / pk["hbm_gbs"], 4)},
+          "convolution_us": {"prefill": round(pt["convolution"], 1), "decode": round(dk["convolution"], 1)},
+        }
+      dense_w = ff_w + proj_w + COMPARE_VOCAB * W
+      out = {"prefill_attention": {"us": round(pt["attention"], 1), "TFLOP/s": round(attn_flops / pt["attention"] / 1e6, 1),
+                                   "frac": round(attn_flops / pt["attention"] / 1e6 / pk["bf16_tflops"], 4)},
+             "decode_attention": {"us": round(dk["attention"], 1), "GB/s": round(attn_bytes / dk["attention"] / 1e3, 1),
+                                  "frac": round(attn_bytes / dk["attention"] / 1e3 / pk["hbm_gbs"], 4)},
+             "prefill_dense_products": {"us": round(pt["dense_products"], 1),
+                                        "TFLOP/s": round(2.0 * T * (ff_w + proj_w) / pt["dense_products"] / 1e6, 1),
+                                        "frac": round(2.0 * T * (ff_w + proj_w) / pt["dense_products"] / 1e6 / pk["bf16_tflops"], 4)},
+             "decode_dense_products": {"us": round(dk["dense_products"], 1), "GB/s": round(2.0 * dense_w / dk["dense_products"] / 1e3, 1),
+                                       "frac": round(2.0 * dense_w / dk["dense_products"] / 1e3 / pk["hbm_gbs"], 4)},
+             "other_us": {"prefill": round(pt["other"], 1), "decode": round(dk["other"], 1)}}
+      out.update(extra)
+    engine.stop()
+    del engine
+    gc.collect()
+    torch.cuda.empty_cache()
+  return out
+
+
 def compare_designs(args) -> int:
-  """``--compare rikanex``: the Rikanex design beside the Qwen3 dense decoder at equal sizes (random weights): prefill of
+  """``--compare rikanex`` / ``--compare vugudra``: the design beside the Qwen3 dense decoder at equal sizes (random weights): prefill of
   one 2048-token prompt and decode steps at ``--batch`` requests with ``--context``-token contexts, and, from a process of
   its own with dependent launch off, what the kinds of kernels of both reach against the measured peaks."""
   pk = peaks()
@@ -810,7 +991,10 @@ def compare_designs(args) -> int:
   GENERATED = max(GENERATED, warmup + args.steps + args.batch * -(-CONTEXT // PREFILL_TOKENS) + 64)
   MAX_MODEL_LEN = max(MAX_MODEL_LEN, -(-(CONTEXT + GENERATED + 128) // 1024) * 1024)
   sizes = [x for x in args.sizes.split(",") if x]
-  result = {"compare": "rikanex beside qwen3 at equal sizes", "batch": args.batch, "context": CONTEXT, "window": COMPARE_WINDOW,
+  design = args.compare
+  sizes_of, configs_of, one = ((COMPARE_SIZES, compare_configs, compare_one) if design == "rikanex" else
+                               (VUGUDRA_SIZES, vugudra_configs, vugudra_one))
+  result = {"compare": f"{design} beside qwen3 at equal sizes", "batch": args.batch, "context": CONTEXT, "window": COMPARE_WINDOW,
             "vocab": COMPARE_VOCAB, "prefill_tokens": PREFILL_TOKENS, "steps": args.steps, "warmup": warmup, "dtype": "bf16",
             "data": "synthetic: random weights, uniform random token ids", "peaks": pk["source"], "sizes": {}}
   kernels_child = args.impl == "compare-child"
@@ -818,22 +1002,22 @@ def compare_designs(args) -> int:
   if clocks:
     clocks.start()
   for tag in sizes:
-    size = COMPARE_SIZES[tag]
+    size = sizes_of[tag]
     row = {"size": size}
-    for name, cfg in compare_configs(size).items():
-      row[name] = compare_one(name, cfg, size, args.batch, args.steps, warmup, pk, kernels_child)
+    for name, cfg in configs_of(size).items():
+      row[name] = one(name, cfg, size, args.batch, args.steps, warmup, pk, kernels_child)
     result["sizes"][tag] = row
   if clocks:
     result["clocks"] = clocks.stop()
   if not kernels_child and not args.skip_kernels:
-    cmd = [sys.executable, os.path.abspath(__file__), "--impl", "compare-child", "--compare", "rikanex", "--sizes", args.sizes,
+    cmd = [sys.executable, os.path.abspath(__file__), "--impl", "compare-child", "--compare", design, "--sizes", args.sizes,
            "--batch", str(args.batch), "--context", str(CONTEXT), "--steps", str(args.steps), "--warmup", str(warmup)]
     proc = subprocess.run(cmd, capture_output=True, text=True, env=dict(os.environ, MINIINFER_B200_PDL="0"))
     found = [l for l in proc.stdout.splitlines() if l.startswith('{"compare"')]
     if found:
       child = json.loads(found[-1])
       for tag in sizes:
-        for name in ("qwen3", "rikanex"):
+        for name in ("qwen3", design):
           result["sizes"][tag][name]["kernels"] = child["sizes"][tag][name]
     else:
       result["kernels_unavailable"] = (proc.stderr or "no output").strip().splitlines()[-1][:300]
@@ -848,8 +1032,8 @@ def main() -> int:
   ap.add_argument("--steps", type=int, default=128)
   ap.add_argument("--warmup", type=int, default=8)
   ap.add_argument("--impl", default="ours", choices=["ours", "reference", "reference-child", "kernels-child", "compare-child"])
-  ap.add_argument("--compare", default=None, choices=["rikanex"],
-                  help="time the Rikanex design beside the Qwen3 dense decoder at equal sizes (--sizes), print one JSON line and exit")
+  ap.add_argument("--compare", default=None, choices=["rikanex", "vugudra"],
+                  help="time the Rikanex or the Vugudra design beside the Qwen3 dense decoder at equal sizes (--sizes), print one JSON line and exit")
   ap.add_argument("--sizes", default="s,m,l", help="with --compare: which of the sizes s, m, l (commas between them)")
   ap.add_argument("--batch", type=int, default=8)
   ap.add_argument("--shape", default="0.6b", choices=sorted(SHAPES), help="layer sizes: the default, or another Qwen3 model's")

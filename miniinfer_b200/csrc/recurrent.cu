@@ -80,6 +80,8 @@ conv_state_kernel(float* __restrict__ state, long long state_stride, const T* __
 //   y[t, c] = (sum_n S[c, n] * C[t, n] + D[c] * u[t, c]) * silu(z[t, c]),      A = -exp(A_log)
 // A channel's states are dealt to P neighbouring lanes, SPT to each; their partial sums meet by shuffles.
 constexpr int SPT = 8;
+constexpr int SCAN_CHUNK = 16;    // tokens whose inputs are fetched together
+constexpr int SCAN_THREADS = 64;
 
 template <typename T>
 struct ScanArgs {
@@ -96,10 +98,10 @@ struct ScanArgs {
 };
 
 template <typename T>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(SCAN_THREADS)
 selective_scan_kernel(ScanArgs<T> a) {
   const int item = blockIdx.y;
-  const int per_block = 128 / a.P;
+  const int per_block = SCAN_THREADS / a.P;
   const int c = blockIdx.x * per_block + threadIdx.x / a.P;
   const int part = threadIdx.x % a.P;
   const int row0 = a.q_start[item], n_new = a.q_len[item], slot = a.seq_slot[item];
@@ -120,25 +122,50 @@ selective_scan_kernel(ScanArgs<T> a) {
     const int n = part * SPT + i;
     S[i] = (live && n < a.N) ? st[n] : 0.f;
   }
-  for (int j = 0; j < n_new; ++j) {
-    const size_t t = (size_t)(row0 + j);
-    const float dt = softplus_f(mi::to_float(a.dt_in[t * a.lddt + cc]) + dtb);
-    const float u = mi::to_float(a.u[t * a.ldu + cc]);
-    const T* brow = a.bc + t * a.ldbc;
-    const float du = dt * u;
-    float acc = 0.f;
-#pragma unroll
-    for (int i = 0; i < SPT; ++i) {
-      const int n = part * SPT + i;
-      if (n < a.N) {
-        S[i] = fmaf(expf(dt * A[i]), S[i], du * mi::to_float(brow[a.b_off + n]));
-        acc = fmaf(S[i], mi::to_float(brow[a.c_off + n]), acc);
-      }
+  // The tokens go by in chunks: a chunk's B and C rows into shared memory and its step sizes, inputs and gates into
+  // registers, all loads issued together, and only then the recurrence over the chunk - so the latency of the loads is
+  // paid once a chunk and not once a token.
+  extern __shared__ float bc_s[];               // [SCAN_CHUNK][2][N]
+  const int N = a.N;
+  for (int c0 = 0; c0 < n_new; c0 += SCAN_CHUNK) {
+    const int n = min(SCAN_CHUNK, n_new - c0);
+    __syncthreads();                            // the chunk before has been read
+    for (int idx = threadIdx.x; idx < n * N; idx += blockDim.x) {
+      const int tt = idx / N, nn = idx % N;
+      const T* brow = a.bc + (size_t)(row0 + c0 + tt) * a.ldbc;
+      bc_s[(tt * 2 + 0) * N + nn] = mi::to_float(brow[a.b_off + nn]);
+      bc_s[(tt * 2 + 1) * N + nn] = mi::to_float(brow[a.c_off + nn]);
     }
-    for (int o = a.P >> 1; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-    if (live && part == 0) {
-      const float zz = mi::to_float(a.z[t * a.ldz + cc]);
-      a.y[t * a.ldy + cc] = mi::from_float<T>((acc + Dc * u) * silu_f(zz));
+    float dtv[SCAN_CHUNK], uv[SCAN_CHUNK], zv[SCAN_CHUNK];
+#pragma unroll
+    for (int tt = 0; tt < SCAN_CHUNK; ++tt) {
+      const size_t t = (size_t)(row0 + c0 + min(tt, n - 1));
+      dtv[tt] = mi::to_float(a.dt_in[t * a.lddt + cc]);
+      uv[tt] = mi::to_float(a.u[t * a.ldu + cc]);
+      zv[tt] = mi::to_float(a.z[t * a.ldz + cc]);
+    }
+    __syncthreads();
+#pragma unroll
+    for (int tt = 0; tt < SCAN_CHUNK; ++tt) {
+      if (tt < n) {
+        const float dt = softplus_f(dtv[tt] + dtb);
+        const float u = uv[tt];
+        const float du = dt * u;
+        const float* Bv = bc_s + (tt * 2 + 0) * N;
+        const float* Cv = bc_s + (tt * 2 + 1) * N;
+        float acc = 0.f;
+#pragma unroll
+        for (int i = 0; i < SPT; ++i) {
+          const int nn = part * SPT + i;
+          if (nn < N) {
+            S[i] = fmaf(expf(dt * A[i]), S[i], du * Bv[nn]);
+            acc = fmaf(S[i], Cv[nn], acc);
+          }
+        }
+        for (int o = a.P >> 1; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+        if (live && part == 0)
+          a.y[(size_t)(row0 + c0 + tt) * a.ldy + cc] = mi::from_float<T>((acc + Dc * u) * silu_f(zv[tt]));
+      }
     }
   }
   if (live) {
@@ -331,7 +358,8 @@ MI_API int mi_selective_scan(void* y, int ldy, const void* u, int ldu, const voi
   if (items == 0) return 0;
   int P = 1;
   while (P * SPT < N) P *= 2;
-  const int per_block = 128 / P;
+  const int per_block = SCAN_THREADS / P;
+  const size_t smem = (size_t)SCAN_CHUNK * 2 * N * sizeof(float);
   dim3 grid((inner + per_block - 1) / per_block, items);
 #define MI_SCAN(TT)                                                                                               \
   do {                                                                                                            \
@@ -340,7 +368,7 @@ MI_API int mi_selective_scan(void* y, int ldy, const void* u, int ldu, const voi
     a.bc = (const TT*)bc; a.ldbc = ldbc; a.b_off = b_off; a.c_off = c_off; a.z = (const TT*)z; a.ldz = ldz;       \
     a.dt_bias = dt_bias; a.A_log = A_log; a.D = D; a.state = state; a.state_stride = state_stride;                \
     a.q_start = q_start; a.q_len = q_len; a.seq_slot = seq_slot; a.inner = inner; a.N = N; a.P = P;               \
-    mi::launch(selective_scan_kernel<TT>, grid, dim3(128), 0, stream, a);                                         \
+    mi::launch(selective_scan_kernel<TT>, grid, dim3(SCAN_THREADS), smem, stream, a);                                         \
   } while (0)
   if (dtype == MI_BF16) MI_SCAN(__nv_bfloat16);
   else if (dtype == MI_F32) MI_SCAN(float);
