@@ -898,7 +898,8 @@ def vugudra_one(name: str, cfg: dict, size: dict, batch: int, steps: int, warmup
       for i in range(4):
         decode(i)
       torch.cuda.synchronize()
-      dk = _vugudra_groups(_kernel_times(lambda i: decode(10 + i), 4))
+      dtimes = _kernel_times(lambda i: decode(10 + i), 4)
+      dk = _vugudra_groups(dtimes)
       for r in rids:
         engine.cache.release_request(r)
       g = torch.Generator().manual_seed(7)
@@ -912,7 +913,8 @@ def vugudra_one(name: str, cfg: dict, size: dict, batch: int, steps: int, warmup
       for i in range(2):
         whole(i)
       torch.cuda.synchronize()
-      pt = _vugudra_groups(_kernel_times(lambda i: whole(10 + i), 2))
+      ptimes = _kernel_times(lambda i: whole(10 + i), 2)
+      pt = _vugudra_groups(ptimes)
       for grp in (pt, dk):
         for key in grp:
           grp[key] = max(grp[key], 1e-9)
@@ -974,6 +976,12 @@ def vugudra_one(name: str, cfg: dict, size: dict, batch: int, steps: int, warmup
                                        "frac": round(2.0 * dense_w / dk["dense_products"] / 1e3 / pk["hbm_gbs"], 4)},
              "other_us": {"prefill": round(pt["other"], 1), "decode": round(dk["other"], 1)}}
       out.update(extra)
+
+      def top(times):
+        rows = sorted(((us, n) for n, us in times.items() if not n.startswith("Mem")), reverse=True)[:14]
+        return [[round(us, 1), n.replace("(anonymous namespace)::", "")[:70]] for us, n in rows]
+
+      out["top_kernels_us"] = {"prefill": top(ptimes), "decode": top(dtimes)}
     engine.stop()
     del engine
     gc.collect()

@@ -342,7 +342,8 @@ decode_split_kernel(DecodeArgs a) {
     const float inv = 1.f / l;
     float acc = 0.f;
     const int first = min(n_splits, 32);
-#pragma unroll 4
+    // sixteen loads in flight: with many query heads on a kv head a warp merges dozens of (head, 32 dims) in turn
+#pragma unroll 16
     for (int s = 0; s < first; ++s) {
       const float f = __shfl_sync(0xffffffffu, w_lane, s);
       if (d < HD) acc = fmaf(__ldcg(po + (size_t)s * HD + d), f, acc);

@@ -87,7 +87,64 @@ gemm_batched_kernel(BatchedArgs a) {
   }
 }
 
+// Few rows (a decode step) in bfloat16: the tiled kernel would wait for global memory once per 16 values of k with one
+// block a tile.  Here a warp takes one output column (batch, n): its lanes deal out k, every lane multiplies its values of
+// the weight row with up to 16 rows of x, and the lanes' sums meet by shuffles.  The sum's order differs from the tiled
+// kernel's, so the 32-bit path, whose results must not depend on how a request was cut, does not take this kernel.
+constexpr int FEW_ROWS = 16;
+
+template <typename TO>
+__global__ void __launch_bounds__(128)
+gemm_batched_few_rows_kernel(BatchedArgs a) {
+  mi::grid_dependency_sync();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int n = blockIdx.x * 4 + warp;
+  const int b = blockIdx.y;
+  if (n >= a.N) return;
+  const __nv_bfloat16* x = (const __nv_bfloat16*)a.x + (size_t)b * a.x_batch;
+  const __nv_bfloat16* w = (const __nv_bfloat16*)a.w + (size_t)b * a.w_batch + (size_t)n * a.ldw;
+  float acc[FEW_ROWS];
+#pragma unroll
+  for (int m = 0; m < FEW_ROWS; ++m) acc[m] = 0.f;
+  for (int k = lane; k < a.K; k += 32) {
+    const float wv = __bfloat162float(w[k]);
+#pragma unroll
+    for (int m = 0; m < FEW_ROWS; ++m)
+      if (m < a.M) acc[m] = fmaf(__bfloat162float(x[(size_t)m * a.lda + k]), wv, acc[m]);
+  }
+  TO* out = (TO*)a.out + (size_t)b * a.o_batch;
+#pragma unroll
+  for (int m = 0; m < FEW_ROWS; ++m) {
+    if (m >= a.M) break;
+    float y = mi::warp_sum(acc[m]);
+    if (lane == 0) {
+      if (a.bias) y += a.bias[n];
+      if (a.act == 1) y = y > 20.f ? y : log1pf(expf(y));
+      if (a.row_gate) y *= 1.f / (1.f + expf(-__bfloat162float(((const __nv_bfloat16*)a.row_gate)[(size_t)m * a.gate_stride + b])));
+      out[(size_t)m * a.ldo + n] = mi::from_float<TO>(y);
+    }
+  }
+}
+
 }  // namespace
+
+MI_API int mi_gemm_batched_few_rows(void* out, int out_dtype, const void* x, const void* w, int dtype, int batch, int M, int N, int K,
+                                    int lda, long long x_batch, int ldw, long long w_batch, int ldo, long long o_batch,
+                                    const float* bias, int act, const void* row_gate, int gate_stride, cudaStream_t stream) {
+  MI_REQUIRE(batch > 0 && batch <= 65535 && M >= 0 && M <= FEW_ROWS && N > 0 && K > 0, "gemm_batched_few_rows: bad sizes batch=%d M=%d N=%d K=%d", batch, M, N, K);
+  MI_REQUIRE(dtype == MI_BF16 && lda >= K && ldw >= K && ldo >= N && (act == 0 || act == 1), "gemm_batched_few_rows: bfloat16 operands, rows that do not overlap");
+  if (M == 0) return 0;
+  BatchedArgs a;
+  a.x = x; a.w = w; a.out = out; a.x_batch = x_batch; a.w_batch = w_batch; a.o_batch = o_batch;
+  a.lda = lda; a.ldw = ldw; a.ldo = ldo; a.M = M; a.N = N; a.K = K; a.bias = bias; a.act = act;
+  a.row_gate = row_gate; a.gate_stride = gate_stride;
+  dim3 grid((N + 3) / 4, batch);
+  if (out_dtype == MI_BF16) mi::launch(gemm_batched_few_rows_kernel<__nv_bfloat16>, grid, dim3(128), 0, stream, a);
+  else if (out_dtype == MI_F32) mi::launch(gemm_batched_few_rows_kernel<float>, grid, dim3(128), 0, stream, a);
+  else return mi_fail("gemm_batched_few_rows: unknown output dtype %d", out_dtype);
+  MI_LAUNCH_OK("gemm_batched_few_rows");
+  return 0;
+}
 
 MI_API int mi_gemm_batched(void* out, int out_dtype, const void* x, const void* w, int dtype, int batch, int M, int N, int K,
                            int lda, long long x_batch, int ldw, long long w_batch, int ldo, long long o_batch,

@@ -78,10 +78,23 @@ conv_state_kernel(float* __restrict__ state, long long state_stride, const T* __
 // Selective scan.  Per channel c and state index n, token after token:
 //   dt = softplus(dt_in[t, c] + dt_bias[c]);  S[c, n] <- exp(dt * A[c, n]) * S[c, n] + dt * u[t, c] * B[t, n]
 //   y[t, c] = (sum_n S[c, n] * C[t, n] + D[c] * u[t, c]) * silu(z[t, c]),      A = -exp(A_log)
-// A channel's states are dealt to P neighbouring lanes, SPT to each; their partial sums meet by shuffles.
-constexpr int SPT = 8;
+// A channel's states are dealt to P neighbouring lanes, SPT to each (up to 32 * SPT states); their partial sums meet by shuffles.
+constexpr int SPT = 4;
 constexpr int SCAN_CHUNK = 16;    // tokens whose inputs are fetched together
 constexpr int SCAN_THREADS = 64;
+
+// The float32 path takes the library's functions; the bfloat16 path the hardware's exponential, logarithm and
+// reciprocal, whose errors (a few units in the last place of float32) are far below the rounding of the activations.
+template <typename T> struct Math {
+  static __device__ __forceinline__ float exp(float x) { return expf(x); }
+  static __device__ __forceinline__ float softplus(float z) { return softplus_f(z); }
+  static __device__ __forceinline__ float silu(float z) { return silu_f(z); }
+};
+template <> struct Math<__nv_bfloat16> {
+  static __device__ __forceinline__ float exp(float x) { return __expf(x); }
+  static __device__ __forceinline__ float softplus(float z) { return z > 20.f ? z : __logf(1.f + __expf(z)); }
+  static __device__ __forceinline__ float silu(float z) { return __fdividef(z, 1.f + __expf(-z)); }
+};
 
 template <typename T>
 struct ScanArgs {
@@ -145,26 +158,40 @@ selective_scan_kernel(ScanArgs<T> a) {
       zv[tt] = mi::to_float(a.z[t * a.ldz + cc]);
     }
     __syncthreads();
+    // four tokens at a time: first what does not depend on the state - step sizes, decays, gates, all independent of one
+    // another - then the recurrence itself, which is multiply-adds only
 #pragma unroll
-    for (int tt = 0; tt < SCAN_CHUNK; ++tt) {
-      if (tt < n) {
-        const float dt = softplus_f(dtv[tt] + dtb);
-        const float u = uv[tt];
-        const float du = dt * u;
-        const float* Bv = bc_s + (tt * 2 + 0) * N;
-        const float* Cv = bc_s + (tt * 2 + 1) * N;
-        float acc = 0.f;
+    for (int t4 = 0; t4 < SCAN_CHUNK; t4 += 4) {
+      if (t4 < n) {
+        float dA[4][SPT], du[4], gz[4];
 #pragma unroll
-        for (int i = 0; i < SPT; ++i) {
-          const int nn = part * SPT + i;
-          if (nn < N) {
-            S[i] = fmaf(expf(dt * A[i]), S[i], du * Bv[nn]);
-            acc = fmaf(S[i], Cv[nn], acc);
+        for (int q = 0; q < 4; ++q) {
+          const float dt = Math<T>::softplus(dtv[t4 + q] + dtb);
+          du[q] = dt * uv[t4 + q];
+          gz[q] = Math<T>::silu(zv[t4 + q]);
+#pragma unroll
+          for (int i = 0; i < SPT; ++i) dA[q][i] = Math<T>::exp(dt * A[i]);
+        }
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const int tt = t4 + q;
+          if (tt < n) {
+            const float* Bv = bc_s + (tt * 2 + 0) * N;
+            const float* Cv = bc_s + (tt * 2 + 1) * N;
+            float acc = 0.f;
+#pragma unroll
+            for (int i = 0; i < SPT; ++i) {
+              const int nn = part * SPT + i;
+              if (nn < N) {
+                S[i] = fmaf(dA[q][i], S[i], du[q] * Bv[nn]);
+                acc = fmaf(S[i], Cv[nn], acc);
+              }
+            }
+            for (int o = a.P >> 1; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+            if (live && part == 0)
+              a.y[(size_t)(row0 + c0 + tt) * a.ldy + cc] = mi::from_float<T>((acc + Dc * uv[tt]) * gz[q]);
           }
         }
-        for (int o = a.P >> 1; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-        if (live && part == 0)
-          a.y[(size_t)(row0 + c0 + tt) * a.ldy + cc] = mi::from_float<T>((acc + Dc * u) * silu_f(zv[tt]));
       }
     }
   }
@@ -183,43 +210,100 @@ selective_scan_kernel(ScanArgs<T> a) {
 //   g[i] = exp(-exp(A_log[head]) * softplus(a[t, head, i] + dt_bias[head, i])),    beta = sigmoid(b[t, head])
 //   S[i, :] <- g[i] * S[i, :];   u = beta * (v - S^T kh);   S <- S + kh u^T;   o = S^T qh
 //   out[t, head, :] = o / sqrt(mean(o^2) + eps) * norm_w * sigmoid(gate[t, head, :])
-// A block per (item, head).  Thread (j, r) keeps rows r * DK .. r * DK + DK - 1 of column j of S in registers; the R
-// threads of a column are neighbouring lanes.  The tokens go through shared memory in chunks: the chunk's q, k, decays,
-// values and betas are prepared by all threads (a warp per token for the unit norms), then the recurrence runs over the
-// chunk, then the chunk's outputs are normalised and gated (a warp per token).
+// Three kernels.  (1) delta_prepare, a warp per (token, head), all tokens at once: everything of a token that does not
+// depend on the state - unit q and k, decays, beta - as float32 rows.  (2) delta_recurrence, the only part that walks
+// the tokens in order: a block per (item, head, group of value columns).  Thread (j, r) keeps rows r * DK .. r * DK + DK - 1
+// of column j of S in registers; the R threads of a column are neighbouring lanes and add their partial sums by
+// shuffles.  Columns do not depend on one another, so a head's columns are dealt to several blocks; the tokens' vectors
+// go through shared memory in chunks.  The raw read-outs go to a float32 buffer.  (3) delta_output, a warp per
+// (token, head): root mean square over the head, weight, gate.
 template <typename T>
-struct DeltaArgs {
-  T* out; int ldo;                       // [tokens, heads * vdim]
-  const T* q; const T* k; int ldqk;      // rows of the convolved q and k: head g at column g * dim
-  const T* v; int ldv;                   // head h at column h * vdim
+struct DeltaPrepArgs {
+  const T* q; const T* k; int ldqk;      // rows of the convolved q and k: q/k head g at column g * dim
   const T* a; int lda;                   // decay input, head h at column h * dim
   const T* b; int ldb;                   // beta logits, head h at column h
-  const T* gate; int ldg;                // output gate logits, head h at column h * vdim
-  const float* dt_bias; const float* A_log; const float* norm_w;
-  float* state; long long state_stride;  // [slot][heads][dim][vdim]
-  const int* q_start; const int* q_len; const int* seq_slot;
-  int heads, kv_heads, dim, vdim, R, chunk;
-  float eps;
+  const float* dt_bias; const float* A_log;
+  float* qn; float* kn;                  // [tokens, kv_heads * dim]
+  float* g;                              // [tokens, heads * dim]
+  float* beta;                           // [tokens, heads]
+  const T* v; int ldv;                   // values, head h at column h * vdim
+  float* raw;                            // [tokens, heads * vdim]: receives the values as float32 (the recurrence reads a
+                                         // token's values from here and writes its read-outs over them)
+  int T_, heads, kv_heads, dim, vdim;
 };
 
-__device__ __forceinline__ int pad_idx(int i) { return i + (i >> 5); }
+template <typename T>
+__global__ void __launch_bounds__(128)
+delta_prepare_kernel(DeltaPrepArgs<T> a) {
+  mi::grid_dependency_sync();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int t = blockIdx.x;
+  const int units = a.kv_heads + a.heads;
+  for (int u = blockIdx.y * 4 + warp; u < units; u += 4 * gridDim.y) {
+    if (u < a.kv_heads) {
+      const T* q = a.q + (size_t)t * a.ldqk + (size_t)u * a.dim;
+      const T* k = a.k + (size_t)t * a.ldqk + (size_t)u * a.dim;
+      float sq = 0.f, sk = 0.f;
+      for (int i = lane; i < a.dim; i += 32) {
+        const float x = mi::to_float(q[i]), y = mi::to_float(k[i]);
+        sq = fmaf(x, x, sq);
+        sk = fmaf(y, y, sk);
+      }
+      sq = mi::warp_sum(sq);
+      sk = mi::warp_sum(sk);
+      const float fq = rsqrtf((float)a.dim) / sqrtf(sq + 1e-6f), fk = 1.f / sqrtf(sk + 1e-6f);
+      for (int i = lane; i < a.dim; i += 32) {
+        a.qn[((size_t)t * a.kv_heads + u) * a.dim + i] = mi::to_float(q[i]) * fq;
+        a.kn[((size_t)t * a.kv_heads + u) * a.dim + i] = mi::to_float(k[i]) * fk;
+      }
+    } else {
+      const int h = u - a.kv_heads;
+      const float neg_rate = -expf(a.A_log[h]);
+      for (int i = lane; i < a.dim; i += 32) {
+        const float z = mi::to_float(a.a[(size_t)t * a.lda + (size_t)h * a.dim + i]) + a.dt_bias[h * a.dim + i];
+        a.g[((size_t)t * a.heads + h) * a.dim + i] = expf(neg_rate * softplus_f(z));
+      }
+      if (lane == 0) a.beta[(size_t)t * a.heads + h] = sigmoid_f(mi::to_float(a.b[(size_t)t * a.ldb + h]));
+      for (int j = lane; j < a.vdim; j += 32)
+        a.raw[((size_t)t * a.heads + h) * a.vdim + j] = mi::to_float(a.v[(size_t)t * a.ldv + (size_t)h * a.vdim + j]);
+    }
+  }
+}
 
-constexpr int delta_max_threads(int dk) { return dk <= 16 ? 1024 : dk <= 64 ? 512 : 256; }
+// 4 bytes from global to shared memory without a register in between; zeros if not `take`
+__device__ __forceinline__ void copy4(float* dst, const float* src, bool take) {
+  const unsigned d = (unsigned)__cvta_generic_to_shared(dst);
+  const int bytes = take ? 4 : 0;
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(d), "l"(src), "r"(bytes) : "memory");
+}
+
+constexpr int DELTA_THREADS = 128;
+constexpr int DELTA_CHUNK = 16;       // tokens whose vectors are in shared memory at a time
+
+template <typename T>
+struct DeltaArgs {
+  float* raw;                            // [tokens, heads * vdim]: the values in, the read-outs before norm and gate out
+  const float* qn; const float* kn; const float* g; const float* beta;
+  float* state; long long state_stride;  // [slot][heads][dim][vdim]
+  const int* q_start; const int* q_len; const int* seq_slot;
+  int heads, kv_heads, dim, vdim, R;
+};
 
 template <typename T, int DK>
-__global__ void __launch_bounds__(delta_max_threads(DK))
-gated_delta_kernel(DeltaArgs<T> a) {
-  extern __shared__ float sm[];
+__global__ void __launch_bounds__(DELTA_THREADS)
+delta_recurrence_kernel(DeltaArgs<T> a) {
+  extern __shared__ __align__(16) float sm[];
+  constexpr int LD = DK + 4;             // a thread's stretch of a vector, padded: 16-byte loads without bank conflicts
   const int item = blockIdx.y, head = blockIdx.x;
   const int kvh = head / (a.heads / a.kv_heads);
   const int row0 = a.q_start[item], n_new = a.q_len[item], slot = a.seq_slot[item];
   const int R = a.R, dim = a.dim, vdim = a.vdim;
-  const int col = threadIdx.x / R, r = threadIdx.x % R;
+  const int cols = DELTA_THREADS / R;
+  const int cl = threadIdx.x / R, r = threadIdx.x % R;
+  const int col = blockIdx.z * cols + cl;
   const bool live = col < vdim;
-  const int dpad = pad_idx(dim) + 1;
-  // per chunk token: q [dpad], k [dpad], g [dpad], v / out [vdim], beta
-  const int tok_floats = 3 * dpad + vdim + 1;
-  const float neg_rate = -expf(a.A_log[head]);
+  const int vec = R * LD;                                    // floats of one padded vector
+  const int tok_floats = 3 * vec + cols + 4;                 // q, k, g, the block's values, beta
   mi::grid_dependency_sync();
   float* st = a.state + (size_t)slot * a.state_stride + (size_t)head * dim * vdim;
   float S[DK];
@@ -228,97 +312,96 @@ gated_delta_kernel(DeltaArgs<T> a) {
     const int row = r * DK + i;
     S[i] = (live && row < dim) ? st[(size_t)row * vdim + col] : 0.f;
   }
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
-  const float q_scale = rsqrtf((float)dim);
-  for (int c0 = 0; c0 < n_new; c0 += a.chunk) {
-    const int n = min(a.chunk, n_new - c0);
-    __syncthreads();
-    // ---- the chunk's inputs
-    for (int idx = threadIdx.x; idx < n * dim; idx += blockDim.x) {
-      const int tt = idx / dim, i = idx % dim;
+  // The chunks' vectors come by asynchronous copies into two buffers: while a chunk is worked on, the next one is on
+  // its way.  Rows past dim and columns past vdim are filled with zeros (a zero key row and decay leave such a row of S
+  // at zero).
+  const int chunk_floats = DELTA_CHUNK * tok_floats;
+  auto fetch = [&](int c0, float* buf) {
+    const int n = min(DELTA_CHUNK, n_new - c0);
+    for (int idx = threadIdx.x; idx < n * R * DK; idx += DELTA_THREADS) {
+      const int tt = idx / (R * DK), i = idx % (R * DK);
       const size_t t = (size_t)(row0 + c0 + tt);
-      float* base = sm + (size_t)tt * tok_floats;
-      base[pad_idx(i)] = mi::to_float(a.q[t * a.ldqk + kvh * dim + i]);
-      base[dpad + pad_idx(i)] = mi::to_float(a.k[t * a.ldqk + kvh * dim + i]);
-      const float z = mi::to_float(a.a[t * a.lda + head * dim + i]) + a.dt_bias[head * dim + i];
-      base[2 * dpad + pad_idx(i)] = expf(neg_rate * softplus_f(z));
+      float* base = buf + (size_t)tt * tok_floats + (i / DK) * LD + (i % DK);
+      const bool in = i < dim;
+      copy4(base, a.qn + (t * a.kv_heads + kvh) * dim + (in ? i : 0), in);
+      copy4(base + vec, a.kn + (t * a.kv_heads + kvh) * dim + (in ? i : 0), in);
+      copy4(base + 2 * vec, a.g + (t * a.heads + head) * dim + (in ? i : 0), in);
     }
-    for (int idx = threadIdx.x; idx < n * vdim; idx += blockDim.x) {
-      const int tt = idx / vdim, jv = idx % vdim;
-      const size_t t = (size_t)(row0 + c0 + tt);
-      sm[(size_t)tt * tok_floats + 3 * dpad + jv] = mi::to_float(a.v[t * a.ldv + head * vdim + jv]);
+    for (int idx = threadIdx.x; idx < n * cols; idx += DELTA_THREADS) {
+      const int tt = idx / cols, j = idx % cols;
+      const int c = blockIdx.z * cols + j;
+      copy4(buf + (size_t)tt * tok_floats + 3 * vec + j, a.raw + (size_t)(row0 + c0 + tt) * (a.heads * vdim) + head * vdim + (c < vdim ? c : 0), c < vdim);
     }
-    for (int tt = threadIdx.x; tt < n; tt += blockDim.x)
-      sm[(size_t)tt * tok_floats + 3 * dpad + vdim] = sigmoid_f(mi::to_float(a.b[(size_t)(row0 + c0 + tt) * a.ldb + head]));
-    __syncthreads();
-    for (int tt = warp; tt < n; tt += warps) {
-      float* base = sm + (size_t)tt * tok_floats;
-      float sq = 0.f, sk = 0.f;
-      for (int i = lane; i < dim; i += 32) {
-        const float x = base[pad_idx(i)], y = base[dpad + pad_idx(i)];
-        sq = fmaf(x, x, sq);
-        sk = fmaf(y, y, sk);
-      }
-      sq = mi::warp_sum(sq);
-      sk = mi::warp_sum(sk);
-      const float fq = q_scale / sqrtf(sq + 1e-6f), fk = 1.f / sqrtf(sk + 1e-6f);
-      for (int i = lane; i < dim; i += 32) {
-        base[pad_idx(i)] *= fq;
-        base[dpad + pad_idx(i)] *= fk;
-      }
+    for (int tt = threadIdx.x; tt < n; tt += DELTA_THREADS)
+      copy4(buf + (size_t)tt * tok_floats + 3 * vec + cols, a.beta + (size_t)(row0 + c0 + tt) * a.heads + head, true);
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+  if (n_new > 0) fetch(0, sm);
+  for (int c0 = 0, ci = 0; c0 < n_new; c0 += DELTA_CHUNK, ++ci) {
+    const int n = min(DELTA_CHUNK, n_new - c0);
+    float* cur = sm + (size_t)(ci & 1) * chunk_floats;
+    if (c0 + DELTA_CHUNK < n_new) {
+      fetch(c0 + DELTA_CHUNK, sm + (size_t)((ci + 1) & 1) * chunk_floats);      // that buffer's chunk was finished before the barrier below
+      asm volatile("cp.async.wait_group 1;" ::: "memory");
+    } else {
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
     }
     __syncthreads();
-    // ---- the recurrence over the chunk
     for (int tt = 0; tt < n; ++tt) {
-      float* base = sm + (size_t)tt * tok_floats;
-      const float* qv = base;
-      const float* kv = base + dpad;
-      const float* gv = base + 2 * dpad;
-      float ks = 0.f;
+      const float* base = cur + (size_t)tt * tok_floats;
+      const float4* qv = reinterpret_cast<const float4*>(base + r * LD);
+      const float4* kv = reinterpret_cast<const float4*>(base + vec + r * LD);
+      const float4* gv = reinterpret_cast<const float4*>(base + 2 * vec + r * LD);
+      float ks[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-      for (int i = 0; i < DK; ++i) {
-        const int row = r * DK + i;
-        if (row < dim) {
-          S[i] *= gv[pad_idx(row)];
-          ks = fmaf(kv[pad_idx(row)], S[i], ks);
-        }
+      for (int i = 0; i < DK / 4; ++i) {
+        const float4 g4 = gv[i], k4 = kv[i];
+        S[4 * i] *= g4.x; S[4 * i + 1] *= g4.y; S[4 * i + 2] *= g4.z; S[4 * i + 3] *= g4.w;
+        ks[0] = fmaf(k4.x, S[4 * i], ks[0]); ks[1] = fmaf(k4.y, S[4 * i + 1], ks[1]);
+        ks[2] = fmaf(k4.z, S[4 * i + 2], ks[2]); ks[3] = fmaf(k4.w, S[4 * i + 3], ks[3]);
       }
-      for (int o = R >> 1; o > 0; o >>= 1) ks += __shfl_xor_sync(0xffffffffu, ks, o);
-      const float vj = live ? base[3 * dpad + col] : 0.f;
-      const float u = base[3 * dpad + vdim] * (vj - ks);
-      float oj = 0.f;
+      float kS = (ks[0] + ks[1]) + (ks[2] + ks[3]);
+      for (int o = R >> 1; o > 0; o >>= 1) kS += __shfl_xor_sync(0xffffffffu, kS, o);
+      const float u = base[3 * vec + cols] * (base[3 * vec + cl] - kS);
+      float os[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-      for (int i = 0; i < DK; ++i) {
-        const int row = r * DK + i;
-        if (row < dim) {
-          S[i] = fmaf(kv[pad_idx(row)], u, S[i]);
-          oj = fmaf(qv[pad_idx(row)], S[i], oj);
-        }
+      for (int i = 0; i < DK / 4; ++i) {
+        const float4 k4 = kv[i], q4 = qv[i];
+        S[4 * i] = fmaf(k4.x, u, S[4 * i]); S[4 * i + 1] = fmaf(k4.y, u, S[4 * i + 1]);
+        S[4 * i + 2] = fmaf(k4.z, u, S[4 * i + 2]); S[4 * i + 3] = fmaf(k4.w, u, S[4 * i + 3]);
+        os[0] = fmaf(q4.x, S[4 * i], os[0]); os[1] = fmaf(q4.y, S[4 * i + 1], os[1]);
+        os[2] = fmaf(q4.z, S[4 * i + 2], os[2]); os[3] = fmaf(q4.w, S[4 * i + 3], os[3]);
       }
+      float oj = (os[0] + os[1]) + (os[2] + os[3]);
       for (int o = R >> 1; o > 0; o >>= 1) oj += __shfl_xor_sync(0xffffffffu, oj, o);
-      // the value's place is free once every thread of the column has read it: all R of them sit in this warp
-      __syncwarp();
-      if (live && r == 0) base[3 * dpad + col] = oj;
+      if (live && r == 0) a.raw[(size_t)(row0 + c0 + tt) * (a.heads * vdim) + head * vdim + col] = oj;
     }
-    __syncthreads();
-    // ---- the chunk's outputs: unit root mean square over the head, weight, gate
-    for (int tt = warp; tt < n; tt += warps) {
-      const float* o = sm + (size_t)tt * tok_floats + 3 * dpad;
-      const size_t t = (size_t)(row0 + c0 + tt);
-      float ss = 0.f;
-      for (int jv = lane; jv < vdim; jv += 32) ss = fmaf(o[jv], o[jv], ss);
-      ss = mi::warp_sum(ss);
-      const float rstd = 1.f / sqrtf(ss / (float)vdim + a.eps);
-      for (int jv = lane; jv < vdim; jv += 32) {
-        const float gl = mi::to_float(a.gate[t * a.ldg + head * vdim + jv]);
-        a.out[t * a.ldo + head * vdim + jv] = mi::from_float<T>(o[jv] * rstd * a.norm_w[jv] * sigmoid_f(gl));
-      }
-    }
+    __syncthreads();      // everyone is done with this buffer before the fetch after next fills it
   }
 #pragma unroll
   for (int i = 0; i < DK; ++i) {
     const int row = r * DK + i;
     if (live && row < dim) st[(size_t)row * vdim + col] = S[i];
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(128)
+delta_output_kernel(T* __restrict__ out, int ldo, const float* __restrict__ raw, const T* __restrict__ gate, int ldg,
+                    const float* __restrict__ norm_w, int heads, int vdim, float eps) {
+  mi::grid_dependency_sync();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int t = blockIdx.x;
+  for (int h = blockIdx.y * 4 + warp; h < heads; h += 4 * gridDim.y) {
+    const float* o = raw + ((size_t)t * heads + h) * vdim;
+    float ss = 0.f;
+    for (int j = lane; j < vdim; j += 32) ss = fmaf(o[j], o[j], ss);
+    ss = mi::warp_sum(ss);
+    const float rstd = 1.f / sqrtf(ss / (float)vdim + eps);
+    for (int j = lane; j < vdim; j += 32) {
+      const float gl = mi::to_float(gate[(size_t)t * ldg + h * vdim + j]);
+      out[(size_t)t * ldo + h * vdim + j] = mi::from_float<T>(o[j] * rstd * norm_w[j] * sigmoid_f(gl));
+    }
   }
 }
 
@@ -378,51 +461,67 @@ MI_API int mi_selective_scan(void* y, int ldy, const void* u, int ldu, const voi
   return 0;
 }
 
+// scratch: float32, tokens * (2 * kv_heads * dim + heads * dim + heads + heads * vdim) values (mi_gated_delta_scratch_floats)
+MI_API long long mi_gated_delta_scratch_floats(int T, int heads, int kv_heads, int dim, int vdim) {
+  return (long long)T * ((long long)2 * kv_heads * dim + (long long)heads * dim + heads + (long long)heads * vdim);
+}
+
 MI_API int mi_gated_delta(void* out, int ldo, const void* q, const void* k, int ldqk, const void* v, int ldv, const void* a_in, int lda,
                           const void* b_in, int ldb, const void* gate, int ldg, int dtype, const float* dt_bias, const float* A_log,
                           const float* norm_w, float eps, float* state, long long state_stride, const int* q_start, const int* q_len,
-                          const int* seq_slot, int items, int heads, int kv_heads, int dim, int vdim, cudaStream_t stream) {
-  MI_REQUIRE(items >= 0 && items <= 65535 && heads > 0 && kv_heads > 0 && heads % kv_heads == 0, "gated_delta: bad head counts %d / %d", heads, kv_heads);
-  MI_REQUIRE(dim > 0 && vdim > 0 && vdim <= 1024 && dim <= 4096, "gated_delta: bad sizes dim=%d vdim=%d", dim, vdim);
+                          const int* seq_slot, int T, int items, int heads, int kv_heads, int dim, int vdim, float* scratch,
+                          cudaStream_t stream) {
+  MI_REQUIRE(T >= 0 && items >= 0 && items <= 65535 && heads > 0 && kv_heads > 0 && heads % kv_heads == 0, "gated_delta: bad head counts %d / %d", heads, kv_heads);
+  MI_REQUIRE(dim > 0 && vdim > 0 && dim <= 4096 && heads <= 65535, "gated_delta: bad sizes dim=%d vdim=%d", dim, vdim);
   MI_REQUIRE(state_stride >= (long long)heads * dim * vdim, "gated_delta: the state rows are too short");
-  if (items == 0) return 0;
-  // rows of a column a thread keeps (DK) and threads a column (R, a power of two up to 32): the smallest DK whose block
-  // fits, so that a thread's share of the state stays in registers
-  int DK = 0, R = 1;
-  for (int dk = 16; dk <= 128 && !DK; dk *= 2) {
-    int r = 1;
-    while (r * dk < dim) r *= 2;
-    if (r <= 32 && ((vdim * r + 31) / 32) * 32 <= delta_max_threads(dk)) { DK = dk; R = r; }
+  MI_REQUIRE(scratch != nullptr && ((uintptr_t)scratch % 16) == 0, "gated_delta: the scratch buffer is missing or unaligned");
+  if (items == 0 || T == 0) return 0;
+  // rows of a column a thread keeps (DK) and threads a column (R, a power of two up to 32)
+  int DK = dim <= 16 ? 16 : 32, R = 1;
+  for (;; DK *= 2) {
+    R = 1;
+    while (R * DK < dim) R *= 2;
+    if (R <= 32 || DK == 128) break;
   }
-  MI_REQUIRE(DK > 0, "gated_delta: a state of %d x %d values a head does not fit a block's registers", dim, vdim);
-  const int threads = ((vdim * R + 31) / 32) * 32;
-  const int dpad = dim + (dim >> 5) + 1;
-  const int tok_floats = 3 * dpad + vdim + 1;
-  int chunk = (40 * 1024 / 4) / tok_floats;
-  if (chunk > 32) chunk = 32;
-  MI_REQUIRE(chunk >= 1, "gated_delta: a token's vectors do not fit shared memory");
-  const size_t smem = (size_t)chunk * tok_floats * sizeof(float);
+  MI_REQUIRE(R <= 32, "gated_delta: dim=%d is more than a block's threads can keep", dim);
+  const int cols = DELTA_THREADS / R;
+  const int tok_floats = 3 * R * (DK + 4) + cols + 4;
+  const size_t smem = (size_t)2 * DELTA_CHUNK * tok_floats * sizeof(float);
+  MI_REQUIRE(smem <= 200 * 1024, "gated_delta: a chunk's vectors (%zu bytes) do not fit shared memory", smem);
+  float* qn = scratch;
+  float* kn = qn + (size_t)T * kv_heads * dim;
+  float* g = kn + (size_t)T * kv_heads * dim;
+  float* beta = g + (size_t)T * heads * dim;
+  float* raw = beta + (((size_t)T * heads + 3) / 4) * 4;
+  dim3 pgrid(T, (heads + kv_heads + 3) / 4 > 16 ? 16 : (heads + kv_heads + 3) / 4);
+  dim3 ogrid(T, (heads + 3) / 4 > 16 ? 16 : (heads + 3) / 4);
+  dim3 rgrid(heads, items, (vdim + cols - 1) / cols);
 #define MI_DELTA(TT, DKV)                                                                                         \
   do {                                                                                                            \
     DeltaArgs<TT> d;                                                                                              \
-    d.out = (TT*)out; d.ldo = ldo; d.q = (const TT*)q; d.k = (const TT*)k; d.ldqk = ldqk; d.v = (const TT*)v; d.ldv = ldv; \
-    d.a = (const TT*)a_in; d.lda = lda; d.b = (const TT*)b_in; d.ldb = ldb; d.gate = (const TT*)gate; d.ldg = ldg; \
-    d.dt_bias = dt_bias; d.A_log = A_log; d.norm_w = norm_w; d.state = state; d.state_stride = state_stride;      \
-    d.q_start = q_start; d.q_len = q_len; d.seq_slot = seq_slot; d.heads = heads; d.kv_heads = kv_heads; d.dim = dim; \
-    d.vdim = vdim; d.R = R; d.chunk = chunk; d.eps = eps;                                                         \
-    mi::launch(gated_delta_kernel<TT, DKV>, dim3(heads, items), dim3(threads), smem, stream, d);                  \
+    d.raw = raw; d.qn = qn; d.kn = kn; d.g = g; d.beta = beta;                                                    \
+    d.state = state; d.state_stride = state_stride; d.q_start = q_start; d.q_len = q_len; d.seq_slot = seq_slot;  \
+    d.heads = heads; d.kv_heads = kv_heads; d.dim = dim; d.vdim = vdim; d.R = R;                                  \
+    if (smem > 48 * 1024) cudaFuncSetAttribute(delta_recurrence_kernel<TT, DKV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+    mi::launch(delta_recurrence_kernel<TT, DKV>, rgrid, dim3(DELTA_THREADS), smem, stream, d);                    \
   } while (0)
-#define MI_DELTA_DK(TT)                 \
-  do {                                  \
-    if (DK == 16) MI_DELTA(TT, 16);     \
-    else if (DK == 32) MI_DELTA(TT, 32); \
-    else if (DK == 64) MI_DELTA(TT, 64); \
-    else MI_DELTA(TT, 128);             \
+#define MI_DELTA_ALL(TT)                                                                                          \
+  do {                                                                                                            \
+    DeltaPrepArgs<TT> p;                                                                                          \
+    p.q = (const TT*)q; p.k = (const TT*)k; p.ldqk = ldqk; p.a = (const TT*)a_in; p.lda = lda; p.b = (const TT*)b_in; p.ldb = ldb; \
+    p.dt_bias = dt_bias; p.A_log = A_log; p.qn = qn; p.kn = kn; p.g = g; p.beta = beta; p.T_ = T; p.heads = heads;  \
+    p.kv_heads = kv_heads; p.dim = dim; p.v = (const TT*)v; p.ldv = ldv; p.raw = raw; p.vdim = vdim;                  \
+    mi::launch(delta_prepare_kernel<TT>, pgrid, dim3(128), 0, stream, p);                                         \
+    if (DK == 16) MI_DELTA(TT, 16);                                                                               \
+    else if (DK == 32) MI_DELTA(TT, 32);                                                                          \
+    else if (DK == 64) MI_DELTA(TT, 64);                                                                          \
+    else MI_DELTA(TT, 128);                                                                                       \
+    mi::launch(delta_output_kernel<TT>, ogrid, dim3(128), 0, stream, (TT*)out, ldo, (const float*)raw, (const TT*)gate, ldg, norm_w, heads, vdim, eps); \
   } while (0)
-  if (dtype == MI_BF16) MI_DELTA_DK(__nv_bfloat16);
-  else if (dtype == MI_F32) MI_DELTA_DK(float);
+  if (dtype == MI_BF16) MI_DELTA_ALL(__nv_bfloat16);
+  else if (dtype == MI_F32) MI_DELTA_ALL(float);
   else return mi_fail("gated_delta: unknown dtype %d", dtype);
-#undef MI_DELTA_DK
+#undef MI_DELTA_ALL
 #undef MI_DELTA
   MI_LAUNCH_OK("gated_delta");
   return 0;

@@ -500,7 +500,8 @@ def linear_batched(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, bias: Op
     if row_gate.dim() != 2 or row_gate.shape[0] != M or row_gate.shape[1] < B or row_gate.stride(1) != 1 or row_gate.dtype != x.dtype:
       raise KernelError("linear_batched: the row gate must hold a logit per row and batch, in the operands' dtype")
     gate_stride = row_gate.stride(0)
-  _check(lib, lib.mi_gemm_batched(
+  few = M <= 16 and x.dtype == torch.bfloat16
+  _check(lib, (lib.mi_gemm_batched_few_rows if few else lib.mi_gemm_batched)(
     ctypes.c_void_p(out.data_ptr()), _dt(out), ctypes.c_void_p(x.data_ptr()), ctypes.c_void_p(w.data_ptr()), _dt(x), B, M, N, K,
     int(x.stride(0)), ctypes.c_longlong(x.stride(1)), int(w.stride(1)), ctypes.c_longlong(w.stride(0)),
     int(out.stride(0)), ctypes.c_longlong(out.stride(1)), _ptr(bias, torch.float32) if bias is not None else _ptr(None),
@@ -551,12 +552,14 @@ def selective_scan(y: torch.Tensor, u: torch.Tensor, dt_in: torch.Tensor, bc: to
 
 def gated_delta(out: torch.Tensor, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, a: torch.Tensor, b: torch.Tensor, gate: torch.Tensor,
                 dt_bias: torch.Tensor, A_log: torch.Tensor, norm_w: torch.Tensor, eps: float, state: torch.Tensor, ctx,
-                heads: int, kv_heads: int, dim: int, vdim: int) -> None:
+                heads: int, kv_heads: int, dim: int, vdim: int, workspace=None) -> None:
   """The gated delta rule over each item's new tokens, from and to the per-request state ``[slots, >= heads * dim * vdim]``
   float32.  ``q``, ``k`` ``[T, kv_heads * dim]`` (convolved and activated; made unit vectors here, q also times dim^-1/2),
   ``v [T, heads * vdim]``, ``a [T, heads * dim]`` (decay input: g = exp(-exp(A_log_h) softplus(a + dt_bias))), ``b [T, heads]``
   (beta = sigmoid(b)), ``gate [T, heads * vdim]``; per head ``S <- diag(g) S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q``;
-  ``out = o / rms(o) * norm_w * sigmoid(gate)``.  All operands may be column ranges of wider rows."""
+  ``out = o / rms(o) * norm_w * sigmoid(gate)``.  All operands may be column ranges of wider rows.  Three launches: what
+  does not depend on the state for all tokens at once, the recurrence, the read-outs' norm and gate; float32 scratch
+  between them from ``workspace`` (a ``Workspace``; made here if absent)."""
   lib = common_lib()
   T = v.shape[0]
   if (q.shape != (T, kv_heads * dim) or k.shape != q.shape or v.shape != (T, heads * vdim) or a.shape != (T, heads * dim) or b.shape != (T, heads)
@@ -569,11 +572,15 @@ def gated_delta(out: torch.Tensor, q: torch.Tensor, k: torch.Tensor, v: torch.Te
   (op, ldo), (qp, ldq), (kp, ldk), (vp, ldv), (ap, lda), (bp, ldb), (gp, ldg) = (_cols(t, "gated_delta") for t in (out, q, k, v, a, b, gate))
   if ldq != ldk:
     raise KernelError("gated_delta: q and k must be column ranges of rows of one width")
+  lib.mi_gated_delta_scratch_floats.restype = ctypes.c_longlong
+  n = int(lib.mi_gated_delta_scratch_floats(T, heads, kv_heads, dim, vdim)) + 8
+  scratch = workspace.buffer("gated_delta_scratch", (n,), torch.float32) if workspace is not None else \
+    torch.empty(n, dtype=torch.float32, device=v.device)
   _check(lib, lib.mi_gated_delta(op, ldo, qp, kp, ldq, vp, ldv, ap, lda, bp, ldb, gp, ldg, _dt(v), _ptr(dt_bias, torch.float32),
                                  _ptr(A_log, torch.float32), _ptr(norm_w, torch.float32), ctypes.c_float(eps),
                                  ctypes.c_void_p(state.data_ptr()), ctypes.c_longlong(state.stride(0)), _ptr(ctx.q_start, torch.int32),
-                                 _ptr(ctx.q_len, torch.int32), _ptr(ctx.seq_slot, torch.int32), ctx.num_items, heads, kv_heads, dim, vdim,
-                                 _stream()))
+                                 _ptr(ctx.q_len, torch.int32), _ptr(ctx.seq_slot, torch.int32), T, ctx.num_items, heads, kv_heads, dim, vdim,
+                                 _ptr(scratch, torch.float32), _stream()), kernels=3)
 
 
 def latent_down(down: torch.Tensor, q_off: int, kv_off: int, q_rank: int, kv_rank: int, rot_dim: int, q_weight: torch.Tensor,
@@ -1031,6 +1038,11 @@ def _attention_bf16(out, qkv, kv_layer, block_table, batch, nh, nkv, hd, scale, 
       max_splits = min(-(-span // 64) + 2, _num_sms(qkv.device))
     else:
       chunk = batch.decode_chunk or decode_chunk(batch.num_decode, nkv, span, hd)
+      if G > 8 and not batch.decode_chunk:
+        # many query heads on one kv head (a latent's shared key/value head): the block that merges a request's pieces has
+        # heads x pieces partial rows to add, so fewer, longer pieces (measured on B200, 16 heads of 224 on one kv head,
+        # 8 requests of 2048 keys: 166 / 101 / 82 / 84 us at 64 / 128 / 256 / 512 keys a piece)
+        chunk = max(chunk, 256)
       max_splits = -(-span // chunk) + 1 + -(-opts.keep_first // chunk)
     n = batch.num_decode * nh * max_splits * (hd + 2)
     if batch.scratch is not None:

@@ -67,8 +67,8 @@ class SelectiveScanMixer(Mixer):
       self.w_x_dt, self.w_x_bc = params["w_x"][:self.dt_rank], params["w_x"][self.dt_rank:]
 
   def validate(self, dtype: torch.dtype) -> None:
-    if self.state > 256 or self.taps > 16:
-      raise ValueError(f"{self.name}: the scan kernel takes up to 256 state values a channel and the convolution up to 16 taps "
+    if self.state > 128 or self.taps > 16:
+      raise ValueError(f"{self.name}: the scan kernel takes up to 128 state values a channel and the convolution up to 16 taps "
                        f"(got state={self.state}, conv={self.taps})")
 
   def forward(self, x: torch.Tensor, ctx, cache) -> torch.Tensor:
@@ -156,15 +156,8 @@ class GatedDeltaMixer(Mixer):
   def validate(self, dtype: torch.dtype) -> None:
     if self.taps > 16:
       raise ValueError(f"{self.name}: the convolution takes up to 16 taps, got {self.taps}")
-    fits = False
-    for dk, most in ((16, 1024), (32, 512), (64, 512), (128, 256)):      # rows a thread keeps, threads a block may have
-      r = 1
-      while r * dk < self.dim:
-        r *= 2
-      fits = fits or (r <= 32 and -(-self.vdim * r // 32) * 32 <= most)
-    if not fits:
-      raise ValueError(f"{self.name}: a state of dim={self.dim} x vdim={self.vdim} values a head does not fit the delta-rule kernel "
-                       f"(for instance 128 x 128 or 256 x 64 do)")
+    if self.dim > 4096:
+      raise ValueError(f"{self.name}: the delta-rule kernel keeps up to 4096 key channels a head, got dim={self.dim}")
 
   def forward(self, x: torch.Tensor, ctx, cache) -> torch.Tensor:
     T = x.shape[0]
@@ -181,7 +174,7 @@ class GatedDeltaMixer(Mixer):
     heads = ctx.ws.buffer("delta_heads", (T, H * Dv), ctx.dtype)
     ops.gated_delta(heads, qkv[:, self.q_off:self.q_off + G * D], qkv[:, self.k_off:self.k_off + G * D], qkv[:, self.v_off:],
                     decay, proj[:, self.b_off:self.b_off + H], gate, self.dt_bias, self.A_log, self.norm, self.norm_eps,
-                    state[:, self.conv_floats:], ctx, H, G, D, Dv)
+                    state[:, self.conv_floats:], ctx, H, G, D, Dv, workspace=ctx.ws)
     out = ctx.ws.buffer(self.out_buffer, (T, self.hidden_size), ctx.dtype)
     ops.linear(out, heads, self.w_o)
     return out

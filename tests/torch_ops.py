@@ -307,7 +307,7 @@ def selective_scan(y, u, dt_in, bc, b_off, c_off, z, dt_bias, A_log, D, state, c
     state[slot, :inner * N] = S.reshape(-1)
 
 
-def gated_delta(out, q, k, v, a, b, gate, dt_bias, A_log, norm_w, eps, state, ctx, heads, kv_heads, dim, vdim):
+def gated_delta(out, q, k, v, a, b, gate, dt_bias, A_log, norm_w, eps, state, ctx, heads, kv_heads, dim, vdim, workspace=None):
   H, G, D, Dv = heads, kv_heads, dim, vdim
   for row0, n, slot in _items(ctx):
     S = state[slot, :H * D * Dv].view(H, D, Dv).clone()
