@@ -856,7 +856,7 @@ def _vugudra_groups(times: dict) -> dict:
       g["head_products"] += us
     elif "selective_scan" in name:
       g["scan"] += us
-    elif "gated_delta" in name:
+    elif "gated_delta" in name or "delta_recurrence" in name or "delta_prepare" in name or "delta_output" in name:
       g["delta_rule"] += us
     elif "causal_conv" in name or "conv_state" in name:
       g["convolution"] += us

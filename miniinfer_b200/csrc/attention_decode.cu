@@ -85,6 +85,7 @@ struct DecodeArgs {
   float* part_ml;                // [n_dec, nh, max_splits, 2]
   int* counters;                 // [n_dec, nkv], zero between launches
   int nh, nkv, page_size, window, chunk, max_splits, keep_first;
+  int merge_apart;               // 1: the pieces are merged by a kernel of its own (decode_merge_kernel)
   float scale;
   const float* sink;             // [nh] or null
   const __nv_bfloat16* gate;     // [T, gate_stride], head h at h * out_hd; or null
@@ -308,6 +309,7 @@ decode_split_kernel(DecodeArgs a) {
     __syncthreads();     // before the next pass overwrites the stages
   }
 
+  if (a.merge_apart) return;
   // ---- the last block of this (request, kv head) merges the chunks
   __threadfence();
   if (threadIdx.x == 0) {
@@ -357,6 +359,39 @@ decode_split_kernel(DecodeArgs a) {
       if (a.gate) y = __fdividef(y, 1.f + __expf(-__bfloat162float(a.gate[(size_t)row * a.gate_stride + (size_t)head * a.out_hd + d])));
       a.out[((size_t)row * a.nh + head) * a.out_hd + d] = __float2bfloat16_rn(y);
     }
+  }
+}
+
+// The merge as a kernel of its own, a block per (request, query head): with many query heads on one kv head the block
+// that finishes a request last would have heads x pieces partial rows to add, one after another.  The same algebra as
+// the merge inside decode_split_kernel, pieces in ascending order; which of the two runs depends on the head counts alone.
+__global__ void __launch_bounds__(128)
+decode_merge_kernel(DecodeArgs a) {
+  mi::grid_dependency_sync();
+  const int head = blockIdx.x, e = blockIdx.y;
+  const int item = a.decode_items[e];
+  const int p = a.ctx_len[item] - 1;
+  const int lo = a.window > 0 ? max(0, p - a.window + 1) : 0;
+  const int kept = a.window > 0 ? min(a.keep_first, lo) : 0;
+  const int n_splits = (kept > 0 ? (kept - 1) / a.chunk + 1 : 0) + p / a.chunk - lo / a.chunk + 1;
+  const int row = a.q_start[item];
+  const float* ml = a.part_ml + ((size_t)e * a.nh + head) * a.max_splits * 2;
+  const float* po = a.part_o + ((size_t)e * a.nh + head) * a.max_splits * HD;
+  float m = -INFINITY;
+  for (int s = 0; s < n_splits; ++s) m = fmaxf(m, ml[2 * s]);
+  const float sink2 = a.sink ? a.sink[head] * 1.4426950408889634f : -INFINITY;
+  m = fmaxf(m, sink2);
+  float l = 0.f;
+  for (int s = 0; s < n_splits; ++s) l = fmaf(ml[2 * s + 1], exp2f(ml[2 * s] - m), l);
+  if (a.sink) l += exp2f(sink2 - m);
+  const float inv = 1.f / l;
+  for (int d = threadIdx.x; d < a.out_hd; d += blockDim.x) {
+    float acc = 0.f;
+#pragma unroll 8
+    for (int s = 0; s < n_splits; ++s) acc = fmaf(po[(size_t)s * HD + d], exp2f(ml[2 * s] - m), acc);
+    float y = acc * inv;
+    if (a.gate) y = __fdividef(y, 1.f + __expf(-__bfloat162float(a.gate[(size_t)row * a.gate_stride + (size_t)head * a.out_hd + d])));
+    a.out[((size_t)row * a.nh + head) * a.out_hd + d] = __float2bfloat16_rn(y);
   }
 }
 
@@ -410,7 +445,10 @@ MI_API int mi_attention_decode_bf16(void* out, const void* q_base, int q_stride,
     if (err != cudaSuccess) return mi_fail("attention_decode: cannot get %zu bytes of shared memory: %s", SMEM_BYTES, cudaGetErrorString(err));
     configured = true;
   }
+  // more than eight query heads on a kv head: the merge as a kernel of its own, a block per (request, head)
+  a.merge_apart = nh / nkv > 8 ? 1 : 0;
   mi::launch(decode_split_kernel, dim3(dim3(nkv, max_splits, n_dec)), dim3(WARPS * 32), SMEM_BYTES, stream, a);
+  if (a.merge_apart) mi::launch(decode_merge_kernel, dim3(nh, n_dec), dim3(128), 0, stream, a);
   MI_LAUNCH_OK("attention_decode");
   return 0;
 }

@@ -80,7 +80,7 @@ conv_state_kernel(float* __restrict__ state, long long state_stride, const T* __
 //   y[t, c] = (sum_n S[c, n] * C[t, n] + D[c] * u[t, c]) * silu(z[t, c]),      A = -exp(A_log)
 // A channel's states are dealt to P neighbouring lanes, SPT to each (up to 32 * SPT states); their partial sums meet by shuffles.
 constexpr int SPT = 4;
-constexpr int SCAN_CHUNK = 16;    // tokens whose inputs are fetched together
+constexpr int SCAN_CHUNK = 16;    // tokens whose inputs are fetched together (32 was measured slower: 1.63 against 1.36 ms for two layers of 2048 tokens)
 constexpr int SCAN_THREADS = 64;
 
 // The float32 path takes the library's functions; the bfloat16 path the hardware's exponential, logarithm and
@@ -143,11 +143,23 @@ selective_scan_kernel(ScanArgs<T> a) {
   for (int c0 = 0; c0 < n_new; c0 += SCAN_CHUNK) {
     const int n = min(SCAN_CHUNK, n_new - c0);
     __syncthreads();                            // the chunk before has been read
-    for (int idx = threadIdx.x; idx < n * N; idx += blockDim.x) {
-      const int tt = idx / N, nn = idx % N;
-      const T* brow = a.bc + (size_t)(row0 + c0 + tt) * a.ldbc;
-      bc_s[(tt * 2 + 0) * N + nn] = mi::to_float(brow[a.b_off + nn]);
-      bc_s[(tt * 2 + 1) * N + nn] = mi::to_float(brow[a.c_off + nn]);
+    for (int i0 = threadIdx.x; i0 < n * N; i0 += 4 * SCAN_THREADS) {      // eight loads in flight a thread
+      float bv[4], cv[4];
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const int idx = min(i0 + q * SCAN_THREADS, n * N - 1);
+        const T* brow = a.bc + (size_t)(row0 + c0 + idx / N) * a.ldbc;
+        bv[q] = mi::to_float(brow[a.b_off + idx % N]);
+        cv[q] = mi::to_float(brow[a.c_off + idx % N]);
+      }
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const int idx = i0 + q * SCAN_THREADS;
+        if (idx < n * N) {
+          bc_s[((idx / N) * 2 + 0) * N + idx % N] = bv[q];
+          bc_s[((idx / N) * 2 + 1) * N + idx % N] = cv[q];
+        }
+      }
     }
     float dtv[SCAN_CHUNK], uv[SCAN_CHUNK], zv[SCAN_CHUNK];
 #pragma unroll
@@ -477,7 +489,7 @@ MI_API int mi_gated_delta(void* out, int ldo, const void* q, const void* k, int 
   MI_REQUIRE(scratch != nullptr && ((uintptr_t)scratch % 16) == 0, "gated_delta: the scratch buffer is missing or unaligned");
   if (items == 0 || T == 0) return 0;
   // rows of a column a thread keeps (DK) and threads a column (R, a power of two up to 32)
-  int DK = dim <= 16 ? 16 : 32, R = 1;
+  int DK = dim <= 128 ? 16 : 32, R = 1;      // measured on B200 at 128 x 128: 16 rows a thread are faster than 32
   for (;; DK *= 2) {
     R = 1;
     while (R * DK < dim) R *= 2;

@@ -1038,11 +1038,6 @@ def _attention_bf16(out, qkv, kv_layer, block_table, batch, nh, nkv, hd, scale, 
       max_splits = min(-(-span // 64) + 2, _num_sms(qkv.device))
     else:
       chunk = batch.decode_chunk or decode_chunk(batch.num_decode, nkv, span, hd)
-      if G > 8 and not batch.decode_chunk:
-        # many query heads on one kv head (a latent's shared key/value head): the block that merges a request's pieces has
-        # heads x pieces partial rows to add, so fewer, longer pieces (measured on B200, 16 heads of 224 on one kv head,
-        # 8 requests of 2048 keys: 166 / 101 / 82 / 84 us at 64 / 128 / 256 / 512 keys a piece)
-        chunk = max(chunk, 256)
       max_splits = -(-span // chunk) + 1 + -(-opts.keep_first // chunk)
     n = batch.num_decode * nh * max_splits * (hd + 2)
     if batch.scratch is not None:
