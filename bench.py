@@ -482,6 +482,31 @@ def kernel_case(name: str, reps: int = 3) -> str:
     out = torch.empty(T, W, dtype=torch.bfloat16, device=dev)
     fn = lambda: ops.routed_experts(out, x, router, corr, gate_up, down, top, ws)
     what = f"{T} tokens, {E} experts of 3 x {F} x {W}, {top} a token ({T * top * 3 * 2 * F * W / 1e9:.1f} GFLOP)"
+  elif name in ("selective_scan", "delta_rule"):
+    # one prompt portion of 8192 tokens (a recurrence walks it in order) beside seven decode tokens of other requests
+    from types import SimpleNamespace
+    cuts = [8192] + [1] * 7
+    T = sum(cuts)
+    it = lambda v: torch.tensor(v, dtype=torch.int32, device=dev)
+    ctx = SimpleNamespace(q_start=it([sum(cuts[:i]) for i in range(len(cuts))]), q_len=it(cuts), seq_slot=it(list(range(len(cuts)))),
+                          num_items=len(cuts), token_item=it([b for b, n in enumerate(cuts) for _ in range(n)]))
+    if name == "selective_scan":
+      inner, N = 4096, 16
+      u, z, dt_in, bc = rnd(T, inner), rnd(T, inner), rnd(T, inner), rnd(T, 2 * N)
+      dt_b, A_log, D = rnd(inner, dtype=torch.float32) - 2.0, rnd(inner, N, dtype=torch.float32).abs(), rnd(inner, dtype=torch.float32)
+      state = torch.zeros((len(cuts), inner * N), dtype=torch.float32, device=dev)
+      y = torch.empty(T, inner, dtype=torch.bfloat16, device=dev)
+      fn = lambda: ops.selective_scan(y, u, dt_in, bc, 0, N, z, dt_b, A_log, D, state, ctx)
+      what = f"{T} tokens ({cuts[0]} of one request), {inner} channels x {N} states ({T * inner * 8 / 1e6:.0f} MB of activations in and out)"
+    else:
+      H, G, Dk, Dv = 16, 8, 128, 128
+      q, k, v = rnd(T, G * Dk), rnd(T, G * Dk), rnd(T, H * Dv)
+      a_in, b_in, gate = rnd(T, H * Dk), rnd(T, H), rnd(T, H * Dv)
+      dt_bias, A_log, norm_w = rnd(H * Dk, dtype=torch.float32) - 1.0, rnd(H, dtype=torch.float32) * 0.3, 1 + 0.1 * rnd(Dv, dtype=torch.float32)
+      state = torch.zeros((len(cuts), H * Dk * Dv), dtype=torch.float32, device=dev)
+      out = torch.empty(T, H * Dv, dtype=torch.bfloat16, device=dev)
+      fn = lambda: ops.gated_delta(out, q, k, v, a_in, b_in, gate, dt_bias, A_log, norm_w, 1e-6, state, ctx, H, G, Dk, Dv, workspace=ws)
+      what = f"{T} tokens ({cuts[0]} of one request), {H} heads of {Dk} x {Dv} on {G} q/k heads"
   else:
     raise SystemExit(f"unknown kernel case {name!r}")
   fn()
@@ -496,7 +521,8 @@ def kernel_case(name: str, reps: int = 3) -> str:
 
 
 KERNEL_CASES = ("sample", "silu_mul", "gemm_f32", "gemm_tc_plain", "gemm_stream", "attention_generic", "attention_prefill_tc",
-                "attention_prefill_tc_pairs", "attention_prefill_mma", "attention_decode_cpasync", "experts_many_rows", "experts_few_rows")
+                "attention_prefill_tc_pairs", "attention_prefill_mma", "attention_decode_cpasync", "experts_many_rows", "experts_few_rows",
+                "selective_scan", "delta_rule")
 
 
 def mixed_workload(model_dir: str, requests: int = 64, outputs: int = 256) -> dict:
