@@ -162,6 +162,7 @@ struct Args {
   const int* seq_slot;
   int* status;
   int n_tiles, nh, nkv, page_size, window;
+  int keep_first;                // with a window: the request's first keep_first keys stay visible (0: none)
   int hpt;                       // query heads of a block: 1 (128 tokens) or 2 (64 tokens each)
   int hw;                        // query heads of a work: hpt, or 2 x hpt when a pair of blocks shares the work
   int skip_odd;                  // hpt = 1 on a list of 64-token tiles: the tiles that start at an odd multiple of 64 are covered by the tile before
@@ -395,6 +396,7 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 // What a block works on at a time: 128 query rows that share one kv head, and the key tiles they see.
 struct Work {
   int item, o, head0, kvh, rows_tok, start, p_first, p_last, lo_last, t_begin, n, row0;
+  int n_first;                   // key tiles of kept first keys that lie before the window's first tile; they are walked first
   const int* bt;
   bool skip;
 };
@@ -420,7 +422,8 @@ __device__ __forceinline__ Work work_of(const Args& a, int w, int rank) {
   const int lo_first = a.window > 0 ? max(0, k.p_first - a.window + 1) : 0;
   k.lo_last = a.window > 0 ? max(0, k.p_last - a.window + 1) : 0;
   k.t_begin = lo_first / BN;
-  k.n = k.p_last / BN - k.t_begin + 1;                    // key tiles to walk
+  k.n_first = (a.window > 0 && a.keep_first > 0) ? min((a.keep_first - 1) / BN + 1, k.t_begin) : 0;
+  k.n = k.n_first + k.p_last / BN - k.t_begin + 1;        // key tiles to walk: the i-th is tile i < n_first ? i : t_begin + i - n_first
   k.row0 = a.q_start[k.item] + k.o;                       // the first row in the step
   k.bt = a.block_table + (size_t)a.seq_slot[k.item] * a.bt_stride;
   return k;
@@ -542,7 +545,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __g
           mbar_wait(values ? &v_empty[s] : &k_empty[s], ((g / STAGES) & 1) ^ 1, abort, a.status);
           unsigned char* dst = kv_s + (size_t)s * R::STAGE + (values ? R::K_HELD : 0);
           if (leader) mbar_expect_tx(full, (uint32_t)K_BYTES);     // of both blocks of a pair together
-          const int key0 = (k.t_begin + li) * BN;
+          const int key0 = (li < k.n_first ? li : k.t_begin + li - k.n_first) * BN;
 #pragma unroll
           for (int pg = 0; pg < 2; ++pg) {
             if (CTAS == 2 && !values && pg != rank) continue;      // K: a block of a pair holds its 64 keys, all dims
@@ -681,8 +684,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __g
       for (int k = 0; k < n_mine; ++k) {
         const int j = 2 * k + st;
         const int kk = base + k;
-        const int key0 = (t_begin + j) * BN;
-        const bool masked = !((t_begin + j) * BN + BN - 1 <= p_first && (t_begin + j) * BN >= lo_last);
+        const int key0 = (j < wk.n_first ? j : t_begin + j - wk.n_first) * BN;
+        const bool masked = j < wk.n_first || !(key0 + BN - 1 <= p_first && key0 >= lo_last);
         mbar_wait(&s_full[st], kk & 1, abort, a.status);
         tc_fence_after();
         float v[BN];
@@ -698,8 +701,10 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __g
           int first = lo_r - key0, last = pos - key0;
           if (last < first) first = BN + 1;                // none: no column passes the test below
           const unsigned span = (unsigned)(last - first);
+          // kept first keys are a second stretch, 0 .. kept - 1 (as far as the row has come), ahead of the window's
+          const int kept = (a.window > 0 ? min(a.keep_first, pos + 1) : 0) - key0;
 #pragma unroll
-          for (int e = 0; e < BN; ++e) v[e] = (unsigned)(e - first) <= span ? v[e] : -INFINITY;
+          for (int e = 0; e < BN; ++e) v[e] = ((unsigned)(e - first) <= span || e < kept) ? v[e] : -INFINITY;
         }
         {
           float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
@@ -934,7 +939,8 @@ MI_API int mi_attention_prefill_tc(void* out, const void* q_map, const void* kv_
                                    const int* tiles, int n_tiles, const int* q_start, const int* q_len, const int* ctx_len,
                                    const int* seq_slot, int* status, int nh, int nkv, int page_size, float scale, int window,
                                    int num_sms, cudaStream_t stream, const int* tiles128, int n_tiles128, int pairs,
-                                   const float* sink, const void* gate, int gate_stride) {
+                                   const float* sink, const void* gate, int gate_stride, int keep_first) {
+  MI_REQUIRE(keep_first >= 0, "attention_prefill_tc: keep_first=%d must not be negative", keep_first);
   MI_REQUIRE(num_sms > 0, "attention_prefill_tc: num_sms");
   MI_REQUIRE(gate == nullptr || (((uintptr_t)gate % 16) == 0 && gate_stride % 8 == 0), "attention_prefill_tc: the gate rows must be 16-byte aligned");
   MI_REQUIRE(n_tiles >= 0 && nh > 0 && nkv > 0 && nh % nkv == 0, "attention_prefill_tc: bad head counts nh=%d nkv=%d", nh, nkv);
@@ -952,7 +958,7 @@ MI_API int mi_attention_prefill_tc(void* out, const void* q_map, const void* kv_
   a.ctx_len = ctx_len;
   a.seq_slot = seq_slot;
   a.status = status;
-  a.n_tiles = n_tiles; a.nh = nh; a.nkv = nkv; a.page_size = page_size; a.window = window;
+  a.n_tiles = n_tiles; a.nh = nh; a.nkv = nkv; a.page_size = page_size; a.window = window; a.keep_first = keep_first;
   a.scale_log2 = scale * 1.4426950408889634f;
   a.sink = sink; a.gate = (const __nv_bfloat16*)gate; a.gate_stride = gate_stride;
   CUtensorMap qm, km;
@@ -993,7 +999,7 @@ MI_API int mi_attention_prefill_tc_supported() { return 0; }
 MI_API int mi_qkv_tensor_map(void*, const void*, long long, long long) { return mi_fail("qkv_tensor_map: head size %d has no tcgen05 kernel", MI_HEAD_DIM); }
 MI_API int mi_attention_prefill_tc(void*, const void*, const void*, const int*, int, const int*, int, const int*, const int*, const int*,
                                    const int*, int*, int, int, int, float, int, int, cudaStream_t, const int*, int, int,
-                                   const float*, const void*, int) {
+                                   const float*, const void*, int, int) {
   return mi_fail("attention_prefill_tc: head size %d has no tcgen05 kernel", MI_HEAD_DIM);
 }
 

@@ -977,12 +977,12 @@ def _attention_bf16(out, qkv, kv_layer, block_table, batch, nh, nkv, hd, scale, 
   lib = attention_lib(hd)
   if opts is None:
     opts = _AttentionOptions(None, None, 0, 0, hd)
-  # the TMA and tcgen05 kernels write whole heads and know windows without kept first keys; sink and gate they take
+  # the TMA and tcgen05 kernels write whole heads; sink and gate they take; kept first keys only the tcgen05 prefill kernel knows
   whole_heads = opts.out_hd == hd and not opts.keep_first
   if batch.num_prefill_tiles:
     # the tcgen05 kernel takes sink and gate; its output rows are whole heads, and it reads the gate 16 bytes at a time
     gate_ok = opts.gate is None or (opts.gate_offset % 8 == 0 and opts.gate_stride % 8 == 0 and opts.gate.data_ptr() % 16 == 0)
-    use_tc = (whole_heads and gate_ok and page_size % 64 == 0 and lib.mi_attention_prefill_tc_supported() == 1
+    use_tc = (opts.out_hd == hd and gate_ok and page_size % 64 == 0 and lib.mi_attention_prefill_tc_supported() == 1
               and os.environ.get("MINIINFER_B200_PREFILL_TC", "1") != "0")
     if use_tc:
       if batch.scratch is not None:
@@ -1000,7 +1000,7 @@ def _attention_bf16(out, qkv, kv_layer, block_table, batch, nh, nkv, hd, scale, 
         _ptr(batch.q_len, torch.int32), _ptr(batch.ctx_len, torch.int32), _ptr(batch.seq_slot, torch.int32),
         _ptr(status, torch.int32), nh, nkv, page_size, ctypes.c_float(scale), win, _num_sms(qkv.device), _stream(),
         _ptr(wide, torch.int32) if wide is not None else _ptr(None), n_wide, pairs,
-        opts.sink_ptr(), opts.gate_ptr(), opts.gate_stride))
+        opts.sink_ptr(), opts.gate_ptr(), opts.gate_stride, opts.keep_first))
       if batch.scratch is None and int(status[0]) != 0:
         raise KernelError("attention_prefill_tc: a bounded wait on a barrier ran out")
     else:

@@ -211,7 +211,7 @@ def _batch(ctx_len, n_new, slot=2):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("hd,page,window,keep", [(32, 16, 20, 3), (80, 64, 75, 19), (64, 64, 100, 70), (48, 8, 33, 17), (16, 16, 7, 1), (32, 16, 40, 0)])
+@pytest.mark.parametrize("hd,page,window,keep", [(32, 16, 20, 3), (80, 64, 75, 19), (64, 64, 100, 70), (128, 64, 300, 130), (128, 64, 70, 5), (64, 64, 129, 128), (48, 8, 33, 17), (16, 16, 7, 1), (32, 16, 40, 0)])
 def test_window_with_kept_first_tokens_edge_keys_stand_out(dtype, hd, page, window, keep):
   """The query of the last token is aligned with ONE key whose score then dominates; the output must be that key's value
   when it is visible - the window's last key, a kept first token, the last kept one - and must not show it when it is
@@ -237,10 +237,11 @@ def test_window_with_kept_first_tokens_edge_keys_stand_out(dtype, hd, page, wind
       # plain: softmax over the visible keys
       kk = keys.to(DT[dtype]).float().repeat_interleave(H // G, dim=1)
       vv = values.to(DT[dtype]).float().repeat_interleave(H // G, dim=1)
-      s = torch.einsum("hd,jhd->hj", q[-1].to(DT[dtype]).float(), kk).masked_fill(~vis[None, :], float("-inf"))
-      want = torch.einsum("hj,jhd->hd", torch.softmax(s, -1), vv).reshape(-1)
+      rows = plain.visible(n, window, keep)[n - n_new:]                      # every row of the portion, not only the last
+      s = torch.einsum("ihd,jhd->hij", q.to(DT[dtype]).float(), kk).masked_fill(~rows[None], float("-inf"))
+      want_all = torch.einsum("hij,jhd->ihd", torch.softmax(s, -1), vv).reshape(n_new, -1)
+      assert float((out.float().cpu() - want_all).abs().max()) <= tol(dtype), f"key {j} (visible: {bool(vis[j])}), {n_new} new tokens"
       got = out[-1].float().cpu()
-      assert float((got - want).abs().max()) <= tol(dtype), f"key {j} (visible: {bool(vis[j])}), {n_new} new tokens"
       near = float((got.view(H, hd) - vv[j]).abs().max()) < 0.05
       assert near == bool(vis[j]), f"key {j}: visible {bool(vis[j])}, but the output {'is' if near else 'is not'} its value"
 
