@@ -108,16 +108,42 @@ struct ScanArgs {
   float* state; long long state_stride;   // [slot][inner][N]
   const int* q_start; const int* q_len; const int* seq_slot;
   int inner, N, P;
+  // segments (MODE 1, 2): an item's new tokens in up to SCAN_SEGMENTS stretches that run side by side
+  float* seg_state;     // [item, segment][inner][N]: MODE 1 writes a stretch's end state from a zero start; the carry kernel
+                        // turns it, in place, into the state the stretch starts from; MODE 2 reads that
+  float* seg_dt;        // [item, segment][inner]: the stretch's sum of step sizes (its decay is exp(A * sum))
 };
 
-template <typename T>
+constexpr int SCAN_SEGMENTS = 16;
+constexpr int SCAN_SEGMENT_MIN = 128;   // tokens a stretch has at least
+
+__device__ __forceinline__ int scan_segments(int n_new) { return max(1, min(SCAN_SEGMENTS, n_new / SCAN_SEGMENT_MIN)); }
+// tokens a stretch of an item (a multiple of the chunk, so that chunks do not straddle stretches)
+__device__ __forceinline__ int scan_segment_len(int n_new, int nseg) { return ((n_new + nseg - 1) / nseg + SCAN_CHUNK - 1) / SCAN_CHUNK * SCAN_CHUNK; }
+
+// MODE 0: an item's tokens in order, from the stored state to the stored state (every sum in an order that depends on
+// the position alone: the 32-bit path, and steps of few tokens).  MODE 1 and 2, for long prompt portions in bfloat16:
+// the item's tokens in stretches side by side - first every stretch from a zero state (1: no output, end state and sum
+// of step sizes kept), then, after the carry kernel has chained the stretches, again from the state it really starts from
+// (2: the outputs).  S_t = a_t S_(t-1) + b_t is linear in S, so a stretch's end state is its decay times the state it
+// starts from plus its end state from zero.
+template <typename T, int MODE>
 __global__ void __launch_bounds__(SCAN_THREADS)
 selective_scan_kernel(ScanArgs<T> a) {
   const int item = blockIdx.y;
   const int per_block = SCAN_THREADS / a.P;
   const int c = blockIdx.x * per_block + threadIdx.x / a.P;
   const int part = threadIdx.x % a.P;
-  const int row0 = a.q_start[item], n_new = a.q_len[item], slot = a.seq_slot[item];
+  int row0 = a.q_start[item], n_new = a.q_len[item];
+  const int slot = a.seq_slot[item];
+  const int seg = MODE == 0 ? 0 : blockIdx.z;
+  if (MODE != 0) {
+    const int nseg = scan_segments(n_new);
+    if (seg >= nseg) return;
+    const int len = scan_segment_len(n_new, nseg);
+    row0 += seg * len;
+    n_new = max(0, min(len, n_new - seg * len));
+  }
   const bool live = c < a.inner;
   const int cc = live ? c : 0;
   float A[SPT];
@@ -128,13 +154,15 @@ selective_scan_kernel(ScanArgs<T> a) {
   }
   const float dtb = a.dt_bias[cc], Dc = a.D[cc];
   mi::grid_dependency_sync();
-  float* st = a.state + (size_t)slot * a.state_stride + (size_t)cc * a.N;
+  float* st = MODE == 0 ? a.state + (size_t)slot * a.state_stride + (size_t)cc * a.N
+                        : a.seg_state + ((size_t)(item * SCAN_SEGMENTS + seg) * a.inner + cc) * a.N;
   float S[SPT];
 #pragma unroll
   for (int i = 0; i < SPT; ++i) {
     const int n = part * SPT + i;
-    S[i] = (live && n < a.N) ? st[n] : 0.f;
+    S[i] = (MODE != 1 && live && n < a.N) ? st[n] : 0.f;
   }
+  float dt_sum = 0.f;
   // The tokens go by in chunks: a chunk's B and C rows into shared memory and its step sizes, inputs and gates into
   // registers, all loads issued together, and only then the recurrence over the chunk - so the latency of the loads is
   // paid once a chunk and not once a token.
@@ -179,6 +207,7 @@ selective_scan_kernel(ScanArgs<T> a) {
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
           const float dt = Math<T>::softplus(dtv[t4 + q] + dtb);
+          if (MODE == 1 && t4 + q < n) dt_sum += dt;
           du[q] = dt * uv[t4 + q];
           gz[q] = Math<T>::silu(zv[t4 + q]);
 #pragma unroll
@@ -199,21 +228,49 @@ selective_scan_kernel(ScanArgs<T> a) {
                 acc = fmaf(S[i], Cv[nn], acc);
               }
             }
-            for (int o = a.P >> 1; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-            if (live && part == 0)
-              a.y[(size_t)(row0 + c0 + tt) * a.ldy + cc] = mi::from_float<T>((acc + Dc * uv[tt]) * gz[q]);
+            if (MODE != 1) {                         // the first pass of the stretches keeps the state only
+              for (int o = a.P >> 1; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+              if (live && part == 0)
+                a.y[(size_t)(row0 + c0 + tt) * a.ldy + cc] = mi::from_float<T>((acc + Dc * uv[tt]) * gz[q]);
+            }
           }
         }
       }
     }
   }
-  if (live) {
+  if (live && MODE != 2) {
 #pragma unroll
     for (int i = 0; i < SPT; ++i) {
       const int n = part * SPT + i;
       if (n < a.N) st[n] = S[i];
     }
+    if (MODE == 1 && part == 0) a.seg_dt[(size_t)(item * SCAN_SEGMENTS + seg) * a.inner + cc] = dt_sum;
   }
+}
+
+// Chains an item's stretches: carry_0 = the stored state, carry_(s+1) = exp(A * dt_sum_s) * carry_s + end_s; the carries
+// replace the end states in seg_state, the last one becomes the stored state.  A thread per (item, channel, state index).
+__global__ void __launch_bounds__(256)
+scan_carry_kernel(float* __restrict__ seg_state, const float* __restrict__ seg_dt, const float* __restrict__ A_log,
+                  float* __restrict__ state, long long state_stride, const int* __restrict__ q_len,
+                  const int* __restrict__ seq_slot, int inner, int N) {
+  const int item = blockIdx.y;
+  const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+  const int nseg = scan_segments(q_len[item]);
+  const int slot = seq_slot[item];
+  mi::grid_dependency_sync();
+  if (idx >= inner * N) return;
+  const int c = idx / N;
+  const float A = -expf(A_log[idx]);
+  float* st = state + (size_t)slot * state_stride + idx;
+  float carry = *st;
+  for (int s = 0; s < nseg; ++s) {
+    float* e = seg_state + (size_t)(item * SCAN_SEGMENTS + s) * inner * N + idx;
+    const float end = *e;
+    *e = carry;
+    carry = fmaf(expf(A * seg_dt[(size_t)(item * SCAN_SEGMENTS + s) * inner + c]), carry, end);
+  }
+  *st = carry;
 }
 
 // ------------------------------------------------------------------------------------------------------------
@@ -444,10 +501,15 @@ MI_API int mi_causal_conv(void* out, int ldo, const void* x, int ldx, int dtype,
   return 0;
 }
 
+MI_API int mi_selective_scan_segments() { return SCAN_SEGMENTS; }
+
 MI_API int mi_selective_scan(void* y, int ldy, const void* u, int ldu, const void* dt_in, int lddt, const void* bc, int ldbc,
                              int b_off, int c_off, const void* z, int ldz, int dtype, const float* dt_bias, const float* A_log,
                              const float* D, float* state, long long state_stride, const int* q_start, const int* q_len,
-                             const int* seq_slot, int items, int inner, int N, cudaStream_t stream) {
+                             const int* seq_slot, int items, int inner, int N, float* segments, cudaStream_t stream) {
+  // segments: null, or items * SCAN_SEGMENTS * inner * (N + 1) floats of scratch - then the items' tokens run in stretches
+  // side by side (bfloat16 only: the sums then depend on where a portion starts)
+  MI_REQUIRE(segments == nullptr || dtype == MI_BF16, "selective_scan: stretches side by side are for bfloat16 activations");
   MI_REQUIRE(items >= 0 && items <= 65535 && inner > 0 && N > 0 && N <= 32 * SPT, "selective_scan: bad sizes inner=%d state=%d (state up to %d)", inner, N, 32 * SPT);
   MI_REQUIRE(state_stride >= (long long)inner * N, "selective_scan: the state rows are too short");
   if (items == 0) return 0;
@@ -463,7 +525,16 @@ MI_API int mi_selective_scan(void* y, int ldy, const void* u, int ldu, const voi
     a.bc = (const TT*)bc; a.ldbc = ldbc; a.b_off = b_off; a.c_off = c_off; a.z = (const TT*)z; a.ldz = ldz;       \
     a.dt_bias = dt_bias; a.A_log = A_log; a.D = D; a.state = state; a.state_stride = state_stride;                \
     a.q_start = q_start; a.q_len = q_len; a.seq_slot = seq_slot; a.inner = inner; a.N = N; a.P = P;               \
-    mi::launch(selective_scan_kernel<TT>, grid, dim3(SCAN_THREADS), smem, stream, a);                                         \
+    a.seg_state = segments; a.seg_dt = segments ? segments + (size_t)items * SCAN_SEGMENTS * inner * N : nullptr; \
+    if (!segments) {                                                                                              \
+      mi::launch(selective_scan_kernel<TT, 0>, grid, dim3(SCAN_THREADS), smem, stream, a);                        \
+    } else {                                                                                                      \
+      dim3 sgrid(grid.x, items, SCAN_SEGMENTS);                                                                   \
+      mi::launch(selective_scan_kernel<TT, 1>, sgrid, dim3(SCAN_THREADS), smem, stream, a);                       \
+      mi::launch(scan_carry_kernel, dim3((inner * N + 255) / 256, items), dim3(256), 0, stream, a.seg_state, (const float*)a.seg_dt, \
+                 A_log, state, state_stride, q_len, seq_slot, inner, N);                                          \
+      mi::launch(selective_scan_kernel<TT, 2>, sgrid, dim3(SCAN_THREADS), smem, stream, a);                       \
+    }                                                                                                             \
   } while (0)
   if (dtype == MI_BF16) MI_SCAN(__nv_bfloat16);
   else if (dtype == MI_F32) MI_SCAN(float);

@@ -529,11 +529,19 @@ def causal_conv(out: torch.Tensor, x: torch.Tensor, weight: torch.Tensor, bias: 
                                  T, ctx.num_items, C, taps, int(bool(silu)), _stream()), kernels=2 if taps > 1 else 1)
 
 
+SCAN_SEGMENTED_MIN_TOKENS = 512    # new tokens a request, on average, from which a bfloat16 scan runs in stretches side by side
+SCAN_SEGMENTED_MAX_ITEMS = 8       # ... in steps of at most this many requests (the scratch grows with them)
+
+
 def selective_scan(y: torch.Tensor, u: torch.Tensor, dt_in: torch.Tensor, bc: torch.Tensor, b_off: int, c_off: int, z: torch.Tensor,
-                   dt_bias: torch.Tensor, A_log: torch.Tensor, D: torch.Tensor, state: torch.Tensor, ctx) -> None:
+                   dt_bias: torch.Tensor, A_log: torch.Tensor, D: torch.Tensor, state: torch.Tensor, ctx, workspace=None) -> None:
   """The selective scan over each item's new tokens, from and to the per-request state ``[slots, >= inner * N]`` float32:
   ``dt = softplus(dt_in + dt_bias)``, ``S[c, n] <- exp(dt_c A[c, n]) S[c, n] + dt_c u_c B_n`` with ``A = -exp(A_log)``,
-  ``y_c = (sum_n S[c, n] C_n + D_c u_c) * silu(z_c)``; B and C are ``N`` columns of ``bc`` from ``b_off`` / ``c_off``."""
+  ``y_c = (sum_n S[c, n] C_n + D_c u_c) * silu(z_c)``; B and C are ``N`` columns of ``bc`` from ``b_off`` / ``c_off``.
+  A bfloat16 step that brings long prompt portions (at least ``SCAN_SEGMENTED_MIN_TOKENS`` a request on average, few
+  requests) runs each request's tokens in up to 16 stretches side by side - every stretch from a zero state, the stretches
+  chained, every stretch again from the state it starts from (three launches, scratch from ``workspace``); a float32 step
+  walks the tokens in order, so that its sums do not depend on how a request was cut."""
   lib = common_lib()
   T, inner = u.shape
   N = A_log.shape[1]
@@ -544,10 +552,18 @@ def selective_scan(y: torch.Tensor, u: torch.Tensor, dt_in: torch.Tensor, bc: to
   if state.dim() != 2 or state.stride(1) != 1 or state.dtype != torch.float32:
     raise KernelError("selective_scan: the state must be float32 rows, one per request slot")
   (yp, ldy), (up, ldu), (dp, ldd), (bp, ldb), (zp, ldz) = (_cols(t, "selective_scan") for t in (y, u, dt_in, bc, z))
+  segments, launches = None, 1
+  if (u.dtype == torch.bfloat16 and ctx.num_items <= SCAN_SEGMENTED_MAX_ITEMS and T >= SCAN_SEGMENTED_MIN_TOKENS * ctx.num_items
+      and os.environ.get("MINIINFER_B200_SCAN_SEGMENTS", "1") != "0"):
+    n = ctx.num_items * int(lib.mi_selective_scan_segments()) * inner * (N + 1)
+    segments = workspace.buffer("selective_scan_segments", (n,), torch.float32) if workspace is not None else \
+      torch.empty(n, dtype=torch.float32, device=u.device)
+    launches = 3
   _check(lib, lib.mi_selective_scan(yp, ldy, up, ldu, dp, ldd, bp, ldb, b_off, c_off, zp, ldz, _dt(u), _ptr(dt_bias, torch.float32),
                                     _ptr(A_log, torch.float32), _ptr(D, torch.float32), ctypes.c_void_p(state.data_ptr()),
                                     ctypes.c_longlong(state.stride(0)), _ptr(ctx.q_start, torch.int32), _ptr(ctx.q_len, torch.int32),
-                                    _ptr(ctx.seq_slot, torch.int32), ctx.num_items, inner, N, _stream()))
+                                    _ptr(ctx.seq_slot, torch.int32), ctx.num_items, inner, N,
+                                    _ptr(segments, torch.float32) if segments is not None else _ptr(None), _stream()), kernels=launches)
 
 
 def gated_delta(out: torch.Tensor, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, a: torch.Tensor, b: torch.Tensor, gate: torch.Tensor,

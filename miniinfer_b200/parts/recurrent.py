@@ -86,7 +86,7 @@ class SelectiveScanMixer(Mixer):
     dt = ctx.ws.buffer("scan_dt", (T, I), ctx.dtype)
     ops.linear(dt, low, self.w_dt)
     y = ctx.ws.buffer("scan_y", (T, I), ctx.dtype)
-    ops.selective_scan(y, u, dt, bc, 0, N, xz[:, I:], self.dt_b, self.A_log, self.D, state[:, self.conv_floats:], ctx)
+    ops.selective_scan(y, u, dt, bc, 0, N, xz[:, I:], self.dt_b, self.A_log, self.D, state[:, self.conv_floats:], ctx, workspace=ctx.ws)
     out = ctx.ws.buffer(self.out_buffer, (T, self.hidden_size), ctx.dtype)
     ops.linear(out, y, self.w_o)
     return out

@@ -99,6 +99,40 @@ def test_selective_scan_against_the_plain_recurrence(dtype, inner, N, rank):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_selective_scan_of_long_portions(dtype):
+  """Portions of hundreds of tokens: in bfloat16 a request's tokens run in stretches side by side that are chained
+  afterwards (the state a stretch starts from is the stored state carried through the stretches before it); the result
+  is the recurrence's, and the state left behind lets the request go on token by token."""
+  from miniinfer_b200.kernels import ops
+  g = torch.Generator().manual_seed(2)
+  inner, N, T = 40, 12, 1500
+  r = lambda *s: torch.randn(s, generator=g)
+  u, z, dt_in, bc = r(T, inner).to(DT[dtype]), r(T, inner).to(DT[dtype]), r(T, inner).to(DT[dtype]), r(T, 2 * N).to(DT[dtype])
+  dt_b, A_log, D = r(inner) - 2.0, torch.log(1 + 3 * torch.rand((inner, N), generator=g)), r(inner)
+  S = torch.zeros(inner, N)
+  want = torch.zeros(T, inner)
+  for t in range(T):
+    dt = torch.nn.functional.softplus(dt_in[t].float() + dt_b)
+    S = torch.exp(dt[:, None] * -torch.exp(A_log)) * S + (dt * u[t].float())[:, None] * bc[t, :N].float()[None, :]
+    want[t] = (S @ bc[t, N:].float() + D * u[t].float()) * plain.silu(z[t].float())
+  for cuts in ((700, 3, 790, 1, 1, 1, 1, 1, 1, 1), (1490,) + (1,) * 10, (520, 515, 465)):
+    state = torch.zeros((3, inner * N), dtype=torch.float32, device=DEV)
+    got = torch.zeros((T, inner), dtype=DT[dtype], device=DEV)
+    pos = 0
+    for n in cuts:
+      sl = slice(pos, pos + n)
+      y = torch.zeros((n, inner), dtype=DT[dtype], device=DEV)
+      ops.selective_scan(y, u[sl].to(DEV), dt_in[sl].to(DEV), bc[sl].to(DEV), 0, N, z[sl].to(DEV), dt_b.to(DEV), A_log.to(DEV),
+                         D.to(DEV), state, step_ctx([n], [1]))
+      got[sl] = y
+      pos += n
+    assert pos == T
+    scale = float(want.abs().max())
+    assert float((got.float().cpu() - want).abs().max()) <= tol(dtype) * max(1.0, scale), f"cut into {cuts}"
+    assert float((state[1].cpu().view(inner, N) - S).abs().max()) <= 1e-3 * max(1.0, float(S.abs().max()))
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("H,G,D,Dv", [(2, 1, 16, 24), (4, 4, 32, 48), (3, 3, 8, 40), (2, 2, 64, 64), (1, 1, 128, 128), (2, 1, 40, 8)])
 def test_gated_delta_rule_against_the_plain_recurrence(dtype, H, G, D, Dv):
   from miniinfer_b200.kernels import ops

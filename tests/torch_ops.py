@@ -293,7 +293,7 @@ def causal_conv(out, x, weight, bias, state, ctx, silu=True):
       state[slot, :S * C] = seq[seq.shape[0] - S:].reshape(-1)
 
 
-def selective_scan(y, u, dt_in, bc, b_off, c_off, z, dt_bias, A_log, D, state, ctx):
+def selective_scan(y, u, dt_in, bc, b_off, c_off, z, dt_bias, A_log, D, state, ctx, workspace=None):
   inner, N = A_log.shape
   A = -torch.exp(A_log.float())
   for row0, n, slot in _items(ctx):
