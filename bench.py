@@ -880,9 +880,9 @@ def _vugudra_groups(times: dict) -> dict:
       g["attention"] += us
     elif "gemm_batched" in name:
       g["head_products"] += us
-    elif "selective_scan" in name:
+    elif "selective_scan" in name or "scan_carry" in name:
       g["scan"] += us
-    elif "gated_delta" in name or "delta_recurrence" in name or "delta_prepare" in name or "delta_output" in name:
+    elif "gated_delta" in name or "delta_recurrence" in name or "delta_prepare" in name or "delta_output" in name or "delta_carry" in name:
       g["delta_rule"] += us
     elif "causal_conv" in name or "conv_state" in name:
       g["convolution"] += us

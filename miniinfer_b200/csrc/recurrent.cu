@@ -356,30 +356,62 @@ struct DeltaArgs {
   float* state; long long state_stride;  // [slot][heads][dim][vdim]
   const int* q_start; const int* q_len; const int* seq_slot;
   int heads, kv_heads, dim, vdim, R;
+  // stretches side by side (MODE 1, 2)
+  float* seg_state;                      // [item, stretch][heads][dim][vdim]: a stretch's end state from a zero start (MODE 1
+                                         // writes), then - after the carry kernel - the state it starts from (MODE 2 reads)
+  float* seg_map;                        // [item, stretch][heads][dim (k)][dim (i)]: the stretch's map of its start state,
+                                         // transposed: end = map * start + end_from_zero
 };
 
-template <typename T, int DK>
+constexpr int DELTA_SEGMENTS = 16;
+constexpr int DELTA_SEGMENT_MIN = 96;    // tokens a stretch has at least
+
+__host__ __device__ __forceinline__ int delta_segments(int n_new) { return max(1, min(DELTA_SEGMENTS, n_new / DELTA_SEGMENT_MIN)); }
+__host__ __device__ __forceinline__ int delta_segment_len(int n_new, int nseg) {
+  return ((n_new + nseg - 1) / nseg + DELTA_CHUNK - 1) / DELTA_CHUNK * DELTA_CHUNK;
+}
+
+// MODE 0: an item's tokens in order, from the stored state to the stored state.  MODE 1 and 2, for long prompt portions in
+// bfloat16: the tokens in stretches side by side.  The state after a token is linear in the state before it - S <-
+// (I - beta k k^T) diag(g) S + beta k v^T - so a stretch's end state is (its map) x (the state it starts from) + (its end state
+// from a zero start).  MODE 1 walks every stretch twice over, in one launch: the value columns from zero with the real
+// values, and dim more columns that start as the identity with zero values - they end as the stretch's map.  The carry
+// kernel chains the stretches; MODE 2 walks every stretch again from the state it really starts from and writes the
+// read-outs.
+template <typename T, int DK, int MODE>
 __global__ void __launch_bounds__(DELTA_THREADS)
 delta_recurrence_kernel(DeltaArgs<T> a) {
   extern __shared__ __align__(16) float sm[];
   constexpr int LD = DK + 4;             // a thread's stretch of a vector, padded: 16-byte loads without bank conflicts
-  const int item = blockIdx.y, head = blockIdx.x;
+  const int item = MODE == 0 ? blockIdx.y : blockIdx.y / DELTA_SEGMENTS, head = blockIdx.x;
+  const int seg = MODE == 0 ? 0 : blockIdx.y % DELTA_SEGMENTS;
   const int kvh = head / (a.heads / a.kv_heads);
-  const int row0 = a.q_start[item], n_new = a.q_len[item], slot = a.seq_slot[item];
+  int row0 = a.q_start[item], n_new = a.q_len[item];
+  const int slot = a.seq_slot[item];
+  if (MODE != 0) {
+    const int nseg = delta_segments(n_new);
+    if (seg >= nseg) return;
+    const int len = delta_segment_len(n_new, nseg);
+    row0 += seg * len;
+    n_new = max(0, min(len, n_new - seg * len));
+  }
   const int R = a.R, dim = a.dim, vdim = a.vdim;
   const int cols = DELTA_THREADS / R;
   const int cl = threadIdx.x / R, r = threadIdx.x % R;
   const int col = blockIdx.z * cols + cl;
-  const bool live = col < vdim;
+  const bool map_col = MODE == 1 && col >= vdim;             // a column of the stretch's map: starts as a unit vector, zero values
+  const bool live = col < vdim + (MODE == 1 ? dim : 0);
   const int vec = R * LD;                                    // floats of one padded vector
   const int tok_floats = 3 * vec + cols + 4;                 // q, k, g, the block's values, beta
   mi::grid_dependency_sync();
-  float* st = a.state + (size_t)slot * a.state_stride + (size_t)head * dim * vdim;
+  const size_t seg_at = ((size_t)(item * DELTA_SEGMENTS + seg) * a.heads + head) * dim;
+  float* st = MODE == 0 ? a.state + (size_t)slot * a.state_stride + (size_t)head * dim * vdim : a.seg_state + seg_at * vdim;
   float S[DK];
 #pragma unroll
   for (int i = 0; i < DK; ++i) {
     const int row = r * DK + i;
-    S[i] = (live && row < dim) ? st[(size_t)row * vdim + col] : 0.f;
+    if (MODE == 1) S[i] = (map_col && row == col - vdim) ? 1.f : 0.f;
+    else S[i] = (live && row < dim) ? st[(size_t)row * vdim + col] : 0.f;
   }
   // The chunks' vectors come by asynchronous copies into two buffers: while a chunk is worked on, the next one is on
   // its way.  Rows past dim and columns past vdim are filled with zeros (a zero key row and decay leave such a row of S
@@ -441,17 +473,75 @@ delta_recurrence_kernel(DeltaArgs<T> a) {
         os[0] = fmaf(q4.x, S[4 * i], os[0]); os[1] = fmaf(q4.y, S[4 * i + 1], os[1]);
         os[2] = fmaf(q4.z, S[4 * i + 2], os[2]); os[3] = fmaf(q4.w, S[4 * i + 3], os[3]);
       }
-      float oj = (os[0] + os[1]) + (os[2] + os[3]);
-      for (int o = R >> 1; o > 0; o >>= 1) oj += __shfl_xor_sync(0xffffffffu, oj, o);
-      if (live && r == 0) a.raw[(size_t)(row0 + c0 + tt) * (a.heads * vdim) + head * vdim + col] = oj;
+      if (MODE != 1) {                        // the first pass of the stretches keeps the state only
+        float oj = (os[0] + os[1]) + (os[2] + os[3]);
+        for (int o = R >> 1; o > 0; o >>= 1) oj += __shfl_xor_sync(0xffffffffu, oj, o);
+        if (live && r == 0) a.raw[(size_t)(row0 + c0 + tt) * (a.heads * vdim) + head * vdim + col] = oj;
+      }
     }
     __syncthreads();      // everyone is done with this buffer before the fetch after next fills it
   }
+  if (MODE != 2) {
 #pragma unroll
-  for (int i = 0; i < DK; ++i) {
-    const int row = r * DK + i;
-    if (live && row < dim) st[(size_t)row * vdim + col] = S[i];
+    for (int i = 0; i < DK; ++i) {
+      const int row = r * DK + i;
+      if (!live || row >= dim) continue;
+      if (map_col) a.seg_map[(seg_at + (col - vdim)) * dim + row] = S[i];    // transposed: [start row k = col - vdim][end row i]
+      else st[(size_t)row * vdim + col] = S[i];
+    }
   }
+}
+
+// Chains an item's stretches, a block per (head, item, group of value columns), a thread per (row i, column j):
+// carry_0 = the stored state, carry_(s+1)[i, j] = sum_k map_s[i, k] carry_s[k, j] + end_s[i, j].  The carries replace
+// the end states in seg_state; the last becomes the stored state.
+constexpr int CARRY_KT = 128;   // rows of the map in shared memory at a time (the whole map up to dim 128)
+
+__global__ void __launch_bounds__(1024)
+delta_carry_kernel(float* __restrict__ seg_state, const float* __restrict__ seg_map, float* __restrict__ state,
+                   long long state_stride, const int* __restrict__ q_len, const int* __restrict__ seq_slot, int heads, int dim,
+                   int vdim, int dimp, int TJ) {
+  extern __shared__ float carry_s[];             // [dim][TJ], then a tile of the map [CARRY_KT][dim]
+  float* map_s = carry_s + dim * TJ;
+  const int head = blockIdx.x, item = blockIdx.y;
+  const int i = threadIdx.x % dimp, jl = threadIdx.x / dimp;
+  const int j = blockIdx.z * TJ + jl;
+  const int nseg = delta_segments(q_len[item]);
+  const int slot = seq_slot[item];
+  mi::grid_dependency_sync();
+  const bool valid = i < dim && j < vdim;
+  float* st = state + (size_t)slot * state_stride + (size_t)head * dim * vdim;
+  float c = valid ? st[(size_t)i * vdim + j] : 0.f;
+  for (int s = 0; s < nseg; ++s) {
+    const size_t at = ((size_t)(item * DELTA_SEGMENTS + s) * heads + head) * dim;
+    float* e = seg_state + at * vdim;
+    const float* m = seg_map + at * dim;
+    if (i < dim) carry_s[i * TJ + jl] = c;
+    __syncthreads();
+    float acc = 0.f;
+    if (valid) {
+      acc = e[(size_t)i * vdim + j];
+      e[(size_t)i * vdim + j] = c;
+    }
+    // the map goes through shared memory in tiles of CARRY_KT of its rows (k), fetched by all threads together
+    for (int k0 = 0; k0 < dim; k0 += CARRY_KT) {
+      const int kn = min(CARRY_KT, dim - k0);
+      for (int i0 = threadIdx.x; i0 < kn * dim; i0 += 8 * blockDim.x) {       // eight loads in flight a thread
+        float mv[8];
+#pragma unroll
+        for (int q = 0; q < 8; ++q) mv[q] = m[(size_t)k0 * dim + min(i0 + q * (int)blockDim.x, kn * dim - 1)];
+#pragma unroll
+        for (int q = 0; q < 8; ++q)
+          if (i0 + q * (int)blockDim.x < kn * dim) map_s[i0 + q * blockDim.x] = mv[q];
+      }
+      __syncthreads();
+      if (valid)
+        for (int k = 0; k < kn; ++k) acc = fmaf(map_s[k * dim + i], carry_s[(k0 + k) * TJ + jl], acc);
+      __syncthreads();
+    }
+    c = acc;
+  }
+  if (valid) st[(size_t)i * vdim + j] = c;
 }
 
 template <typename T>
@@ -549,11 +639,30 @@ MI_API long long mi_gated_delta_scratch_floats(int T, int heads, int kv_heads, i
   return (long long)T * ((long long)2 * kv_heads * dim + (long long)heads * dim + heads + (long long)heads * vdim);
 }
 
+MI_API int mi_gated_delta_segments() { return DELTA_SEGMENTS; }
+
+// Blocks that walk one request's tokens in order (heads x groups of value columns): what a long prompt portion keeps
+// busy without stretches side by side.
+MI_API int mi_gated_delta_blocks(int heads, int dim, int vdim) {
+  int DK = dim <= 128 ? 16 : 32, R = 1;
+  for (;; DK *= 2) {
+    R = 1;
+    while (R * DK < dim) R *= 2;
+    if (R <= 32 || DK == 128) break;
+  }
+  const int cols = DELTA_THREADS / (R > 32 ? 32 : R);
+  return heads * ((vdim + cols - 1) / cols);
+}
+
 MI_API int mi_gated_delta(void* out, int ldo, const void* q, const void* k, int ldqk, const void* v, int ldv, const void* a_in, int lda,
                           const void* b_in, int ldb, const void* gate, int ldg, int dtype, const float* dt_bias, const float* A_log,
                           const float* norm_w, float eps, float* state, long long state_stride, const int* q_start, const int* q_len,
                           const int* seq_slot, int T, int items, int heads, int kv_heads, int dim, int vdim, float* scratch,
-                          cudaStream_t stream) {
+                          float* segments, cudaStream_t stream) {
+  // segments: null, or items * DELTA_SEGMENTS * heads * dim * (vdim + dim) floats of scratch - then the items' tokens run
+  // in stretches side by side (bfloat16 only: the sums then depend on where a portion starts; dim up to 256)
+  MI_REQUIRE(segments == nullptr || (dtype == MI_BF16 && dim <= 256 && items * DELTA_SEGMENTS <= 65535),
+             "gated_delta: stretches side by side are for bfloat16 activations and dim up to 256");
   MI_REQUIRE(T >= 0 && items >= 0 && items <= 65535 && heads > 0 && kv_heads > 0 && heads % kv_heads == 0, "gated_delta: bad head counts %d / %d", heads, kv_heads);
   MI_REQUIRE(dim > 0 && vdim > 0 && dim <= 4096 && heads <= 65535, "gated_delta: bad sizes dim=%d vdim=%d", dim, vdim);
   MI_REQUIRE(state_stride >= (long long)heads * dim * vdim, "gated_delta: the state rows are too short");
@@ -585,8 +694,24 @@ MI_API int mi_gated_delta(void* out, int ldo, const void* q, const void* k, int 
     d.raw = raw; d.qn = qn; d.kn = kn; d.g = g; d.beta = beta;                                                    \
     d.state = state; d.state_stride = state_stride; d.q_start = q_start; d.q_len = q_len; d.seq_slot = seq_slot;  \
     d.heads = heads; d.kv_heads = kv_heads; d.dim = dim; d.vdim = vdim; d.R = R;                                  \
-    if (smem > 48 * 1024) cudaFuncSetAttribute(delta_recurrence_kernel<TT, DKV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
-    mi::launch(delta_recurrence_kernel<TT, DKV>, rgrid, dim3(DELTA_THREADS), smem, stream, d);                    \
+    d.seg_state = segments; d.seg_map = segments ? segments + (size_t)items * DELTA_SEGMENTS * heads * dim * vdim : nullptr; \
+    if (!segments) {                                                                                              \
+      if (smem > 48 * 1024) cudaFuncSetAttribute(delta_recurrence_kernel<TT, DKV, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+      mi::launch(delta_recurrence_kernel<TT, DKV, 0>, rgrid, dim3(DELTA_THREADS), smem, stream, d);               \
+    } else {                                                                                                      \
+      if (smem > 48 * 1024) {                                                                                     \
+        cudaFuncSetAttribute(delta_recurrence_kernel<TT, DKV, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+        cudaFuncSetAttribute(delta_recurrence_kernel<TT, DKV, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+      }                                                                                                           \
+      dim3 g1(heads, items * DELTA_SEGMENTS, (vdim + dim + cols - 1) / cols), g2(heads, items * DELTA_SEGMENTS, rgrid.z); \
+      const int dimp = (dim + 31) / 32 * 32, TJ = 1024 / dimp;                                                    \
+      mi::launch(delta_recurrence_kernel<TT, DKV, 1>, g1, dim3(DELTA_THREADS), smem, stream, d);                  \
+      const size_t csmem = (size_t)dim * (TJ + (dim < CARRY_KT ? dim : CARRY_KT)) * sizeof(float);                \
+      if (csmem > 48 * 1024) cudaFuncSetAttribute(delta_carry_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)csmem); \
+      mi::launch(delta_carry_kernel, dim3(heads, items, (vdim + TJ - 1) / TJ), dim3(dimp * TJ), csmem, stream,    \
+                 d.seg_state, (const float*)d.seg_map, state, state_stride, q_len, seq_slot, heads, dim, vdim, dimp, TJ); \
+      mi::launch(delta_recurrence_kernel<TT, DKV, 2>, g2, dim3(DELTA_THREADS), smem, stream, d);                  \
+    }                                                                                                             \
   } while (0)
 #define MI_DELTA_ALL(TT)                                                                                          \
   do {                                                                                                            \

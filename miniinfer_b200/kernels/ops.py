@@ -531,6 +531,11 @@ def causal_conv(out: torch.Tensor, x: torch.Tensor, weight: torch.Tensor, bias: 
 
 SCAN_SEGMENTED_MIN_TOKENS = 512    # new tokens a request, on average, from which a bfloat16 scan runs in stretches side by side
 SCAN_SEGMENTED_MAX_ITEMS = 8       # ... in steps of at most this many requests (the scratch grows with them)
+DELTA_SEGMENTED_MAX_ITEMS = 4      # the same bound for the delta rule, whose scratch holds a state and a map a stretch and head
+# ... and only while the walk in order would leave most SMs idle: stretches cost three times the arithmetic.  Measured on
+# B200, 2048 tokens of one request, heads of 128 x 128: 8 heads (64 blocks in order) 5.18 -> 4.57 ms a step of six layers,
+# 16 heads (128 blocks) 7.23 -> 8.11 ms
+DELTA_SEGMENTED_MAX_BLOCKS = 96
 
 
 def selective_scan(y: torch.Tensor, u: torch.Tensor, dt_in: torch.Tensor, bc: torch.Tensor, b_off: int, c_off: int, z: torch.Tensor,
@@ -575,7 +580,9 @@ def gated_delta(out: torch.Tensor, q: torch.Tensor, k: torch.Tensor, v: torch.Te
   (beta = sigmoid(b)), ``gate [T, heads * vdim]``; per head ``S <- diag(g) S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q``;
   ``out = o / rms(o) * norm_w * sigmoid(gate)``.  All operands may be column ranges of wider rows.  Three launches: what
   does not depend on the state for all tokens at once, the recurrence, the read-outs' norm and gate; float32 scratch
-  between them from ``workspace`` (a ``Workspace``; made here if absent)."""
+  between them from ``workspace`` (a ``Workspace``; made here if absent).  A bfloat16 step of long prompt portions walks
+  each request's tokens in stretches side by side (``csrc/recurrent.cu``); a float32 step walks them in order, so that its
+  sums do not depend on how a request was cut."""
   lib = common_lib()
   T = v.shape[0]
   if (q.shape != (T, kv_heads * dim) or k.shape != q.shape or v.shape != (T, heads * vdim) or a.shape != (T, heads * dim) or b.shape != (T, heads)
@@ -592,11 +599,21 @@ def gated_delta(out: torch.Tensor, q: torch.Tensor, k: torch.Tensor, v: torch.Te
   n = int(lib.mi_gated_delta_scratch_floats(T, heads, kv_heads, dim, vdim)) + 8
   scratch = workspace.buffer("gated_delta_scratch", (n,), torch.float32) if workspace is not None else \
     torch.empty(n, dtype=torch.float32, device=v.device)
+  # long prompt portions in bfloat16: each request's tokens in up to 16 stretches side by side (five launches instead of three)
+  segments, launches = None, 3
+  if (v.dtype == torch.bfloat16 and ctx.num_items <= DELTA_SEGMENTED_MAX_ITEMS and T >= SCAN_SEGMENTED_MIN_TOKENS * ctx.num_items
+      and dim <= 256 and ctx.num_items * int(lib.mi_gated_delta_blocks(heads, dim, vdim)) <= DELTA_SEGMENTED_MAX_BLOCKS
+      and os.environ.get("MINIINFER_B200_DELTA_SEGMENTS", "1") != "0"):
+    m = ctx.num_items * int(lib.mi_gated_delta_segments()) * heads * dim * (vdim + dim)
+    segments = workspace.buffer("gated_delta_segments", (m,), torch.float32) if workspace is not None else \
+      torch.empty(m, dtype=torch.float32, device=v.device)
+    launches = 5
   _check(lib, lib.mi_gated_delta(op, ldo, qp, kp, ldq, vp, ldv, ap, lda, bp, ldb, gp, ldg, _dt(v), _ptr(dt_bias, torch.float32),
                                  _ptr(A_log, torch.float32), _ptr(norm_w, torch.float32), ctypes.c_float(eps),
                                  ctypes.c_void_p(state.data_ptr()), ctypes.c_longlong(state.stride(0)), _ptr(ctx.q_start, torch.int32),
                                  _ptr(ctx.q_len, torch.int32), _ptr(ctx.seq_slot, torch.int32), T, ctx.num_items, heads, kv_heads, dim, vdim,
-                                 _ptr(scratch, torch.float32), _stream()), kernels=3)
+                                 _ptr(scratch, torch.float32), _ptr(segments, torch.float32) if segments is not None else _ptr(None),
+                                 _stream()), kernels=launches)
 
 
 def latent_down(down: torch.Tensor, q_off: int, kv_off: int, q_rank: int, kv_rank: int, rot_dim: int, q_weight: torch.Tensor,

@@ -171,6 +171,50 @@ def test_gated_delta_rule_against_the_plain_recurrence(dtype, H, G, D, Dv):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("H,G,D,Dv", [(2, 1, 24, 40), (1, 1, 128, 64)])
+def test_gated_delta_rule_of_long_portions(dtype, H, G, D, Dv):
+  """Portions of hundreds of tokens: in bfloat16 a request's tokens run in stretches side by side - each from a zero state
+  and, in further columns that start as the identity, as the map of the state it starts from - which are chained
+  afterwards; the result is the recurrence's, and the state left behind lets the request go on token by token."""
+  from miniinfer_b200.kernels import ops
+  g = torch.Generator().manual_seed(D + Dv)
+  T, eps = 1300, 1e-5
+  r = lambda *s: torch.randn(s, generator=g)
+  q, k, v = r(T, G * D).to(DT[dtype]), r(T, G * D).to(DT[dtype]), r(T, H * Dv).to(DT[dtype])
+  a, b, gate = r(T, H * D).to(DT[dtype]), r(T, H).to(DT[dtype]), r(T, H * Dv).to(DT[dtype])
+  dt_bias, A_log, norm_w = r(H * D) - 3.0, torch.rand((H,), generator=g) - 0.5, 1 + 0.1 * r(Dv)
+  qf, kf = q.float().view(T, G, D), k.float().view(T, G, D)
+  qf = qf / torch.sqrt((qf * qf).sum(-1, keepdim=True) + 1e-6) * D ** -0.5
+  kf = kf / torch.sqrt((kf * kf).sum(-1, keepdim=True) + 1e-6)
+  decay = torch.exp(-torch.exp(A_log)[None, :, None] * torch.nn.functional.softplus(a.float().view(T, H, D) + dt_bias.view(H, D)))
+  beta = torch.sigmoid(b.float())
+  want = torch.zeros(T, H, Dv)
+  last = torch.zeros(H, D, Dv)
+  for h in range(H):
+    S = torch.zeros(D, Dv)
+    for t in range(T):
+      S = decay[t, h][:, None] * S
+      S = S + torch.outer(kf[t, h // (H // G)], beta[t, h] * (v[t].float().view(H, Dv)[h] - S.T @ kf[t, h // (H // G)]))
+      want[t, h] = S.T @ qf[t, h // (H // G)]
+    last[h] = S
+  want = plain.rms_unit(want, eps) * norm_w * torch.sigmoid(gate.float().view(T, H, Dv))
+  for cuts in ((600, 2, 690, 1, 1, 1, 1, 1, 1, 1, 1), (1290,) + (1,) * 10, (520, 780)):
+    state = torch.zeros((3, H * D * Dv), dtype=torch.float32, device=DEV)
+    got = torch.zeros((T, H * Dv), dtype=DT[dtype], device=DEV)
+    pos = 0
+    for n in cuts:
+      sl = slice(pos, pos + n)
+      out = torch.zeros((n, H * Dv), dtype=DT[dtype], device=DEV)
+      ops.gated_delta(out, q[sl].to(DEV), k[sl].to(DEV), v[sl].to(DEV), a[sl].to(DEV), b[sl].to(DEV), gate[sl].to(DEV), dt_bias.to(DEV),
+                      A_log.to(DEV), norm_w.to(DEV), eps, state, step_ctx([n], [2]), H, G, D, Dv)
+      got[sl] = out
+      pos += n
+    assert pos == T
+    assert float((got.float().cpu() - want.reshape(T, -1)).abs().max()) <= tol(dtype) * 2, f"cut into {cuts}"
+    assert float((state[2].cpu().view(H, D, Dv) - last).abs().max()) <= 2e-3 * max(1.0, float(last.abs().max()))
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_two_norms_of_one_row_and_the_mean_of_two_normed_outputs(dtype):
   from miniinfer_b200.kernels import ops
   g = torch.Generator().manual_seed(4)
